@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Benchmark of the one-bit 2:4 sparse GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--size S]
+
+A step is one pass C = A_sparse x B of the square workload a_rows = n = a_cols = S (default 8192,
+the size the >= 60 %-of-sparse-peak target is quoted on) with per-row fp16 scale, fp16 tokens, fp32
+accumulation and fp16 output. With N > 1 every rank owns one S-row slab of A (a_rows = S * N, weak
+scaling, no data-path collective; B replicated). Rank 0 prints ONE JSON line.
+
+  value     dense-equivalent TFLOP/s (2*m*n*k / t), operands resident in HBM, device-timed
+  e2e       the same metric through the Python module's forward with HOST tokens: pinned-host ->
+            device copy of B and device -> pinned-host copy of C inside the timed region (weights
+            stay resident: packing is an offline step, as in the reference)
+  roofline  tensor-core bound; peak = 2 x the measured dense bf16 peak (2:4 sparse MMA rate)
+  cpu_baseline  the CPU oracle (a port of the reference's host check) on a bounded row sample
+
+--impl reference times the reference's CPU implementation of the path (the oracle port: the
+reference's host GEMM needs its absent CUTLASS submodule) on the host cores, same config.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "dense-equivalent TFLOP/s, one-bit 2:4 sparse GEMM (square)"
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.stop = index, [], threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.thread.join(timeout=10)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def cpu_sample(size, rows, threads=0):
+    """Times the oracle GEMM on `rows` weight rows of the size^3 workload; returns (TFLOP/s, seconds, cores)."""
+    import oracle
+    from tests import helpers
+    rng = np.random.default_rng(3080)
+    dense, scale = helpers.make_weights(rng, rows, size)
+    B = helpers.make_tokens(rng, size, size)
+    canon, signs, _ = oracle.compress(dense)
+    bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, oracle.META_CUTLASS)
+    cores = oracle.max_threads() if threads == 0 else threads
+    t0 = time.perf_counter()
+    oracle.gemm(bits, meta, oracle.META_CUTLASS, B, rows, scale=scale, threads=cores)
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * size * size / dt / 1e12, dt, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 512
+    vals = []
+    for i in range(args.warmup + args.steps):
+        v, dt, cores = cpu_sample(args.size, rows)
+        if i >= args.warmup:
+            vals.append((v, dt))
+    v = float(np.mean([x[0] for x in vals]))
+    ms = float(np.mean([x[1] for x in vals])) * 1e3
+    sample = f"{rows} of {args.size} weight rows x full k x full n per step (oracle port, OpenMP)"
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"square {args.size}^3 one-bit 2:4 sparse GEMM", "sample": sample},
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import onebitsparsemul_b200 as ob
+    from onebitsparsemul_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _lib.load()
+    S = args.size
+    m = n = k = S
+    dev = torch.device("cuda", local)
+
+    # synthetic, seeded: random valid 2:4 pattern, Bernoulli signs, scale U[0.01,0.1], tokens N(0,1)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3080 + rank)
+    nib = torch.tensor([0x4, 0x8, 0x9, 0xC, 0xD, 0xE], device=dev)[torch.randint(0, 6, (m, k // 4), device=dev, generator=g)]
+    sign = (torch.randint(0, 2, (m, k // 4, 2), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    w = torch.zeros((m, k // 4, 4), dtype=torch.float16, device=dev)
+    w.scatter_(2, (nib & 3).unsqueeze(-1), sign[..., 0:1])
+    w.scatter_(2, (nib >> 2).unsqueeze(-1), sign[..., 1:2])
+    scale = torch.empty(m, device=dev).uniform_(0.01, 0.1, generator=g).to(torch.float16)
+    layer = ob.BinaryLinear_2_4(k, m, out_dtype=torch.float16).to(dev)
+    t0 = time.perf_counter()
+    layer.pack(w.reshape(m, k), scale=scale)
+    torch.cuda.synchronize()
+    pack_ms = (time.perf_counter() - t0) * 1e3
+    del w, nib, sign
+    B = torch.randn((k, n), device=dev, generator=g, dtype=torch.float32).to(torch.float16)
+    C = torch.empty((m, n), dtype=torch.float16, device=dev)
+    pw = ob.PackedWeight(m, k, layer.bits_tile, layer.meta_tile, layer.scale)
+
+    def step():
+        ob.matmul_packed(pw, B, out=C)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    _lib.check(lib.onebit_check_device_status())
+
+    sync_all()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local) as clocks:
+        ev[0].record()
+        for i in range(args.steps):
+            step()
+            ev[i + 1].record()
+        sync_all()
+    total_ms = ev[0].elapsed_time(ev[-1])
+    kernel_ms = float(np.mean([ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]))
+    t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    _lib.check(lib.onebit_check_device_status())
+    flops_step = 2.0 * m * n * k * world
+    value = flops_step * args.steps / (total_ms * 1e-3) / 1e12
+
+    # end to end: host tokens in, host result out, through the module's forward
+    Bh = B.cpu().pin_memory()
+    Ch = torch.empty((m, n), dtype=torch.float16).pin_memory()
+
+    def e2e_step():
+        x = Bh.to(dev, non_blocking=True)
+        y = layer(x)
+        Ch.copy_(y, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(2, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = flops_step * e2e_steps / (float(t.item()) * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks = load_peaks()
+        sparse_peak = 2.0 * peaks["bf16_tflops"]
+        achieved = 2.0 * m * n * k / (kernel_ms * 1e-3) / 1e12
+        cpu_v, cpu_dt, cores = cpu_sample(S, 2048)
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": f"square one-bit 2:4 sparse GEMM a_rows={S * world} n={S} a_cols={S} (config 1), "
+                                   f"{S}-row slab of A per GPU, fp16 tokens N(0,1), per-row fp16 scale, fp16 out",
+                       "l2": "inputs larger than L2 (B and C 2*S*S bytes each)", "pack_ms": pack_ms},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": Bh.numel() * 2, "d2h_bytes_per_step": Ch.numel() * 2,
+                    "note": "tokens from pinned host memory, result to pinned host memory, weights resident"},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": sparse_peak, "unit": "TFLOP/s",
+                         "frac": achieved / sparse_peak, "traffic": None,
+                         "peak_note": f"2 x dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}): 2:4 sparse MMA rate",
+                         "frac_of_dense_peak": achieved / peaks["bf16_tflops"], "kernel": "ob_gemm_prefill_kernel",
+                         "kernel_ms": kernel_ms},
+            "cpu_baseline": {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": f"2048 of {S} weight rows x full k x full n ({cpu_dt:.2f} s)"},
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=8192)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

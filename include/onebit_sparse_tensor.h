@@ -1,0 +1,120 @@
+/*
+ * libonebitmul -- C = A_sparse x B on NVIDIA B200 (sm_100a).
+ *   A : one-bit (+-1) 2:4 structured-sparse weight matrix, m x k, 1.5 bit per dense weight,
+ *       optional per-row fp16 scale
+ *   B : dense fp16 activations, k x n row-major (n contiguous)
+ *   C : m x n row-major, fp32 or fp16, fp32 accumulation
+ *
+ * This header is the drop-in boundary for the reference's include/onebit_sparse_tensor.h. The first
+ * declaration keeps the reference's exact signature and C++ linkage; everything inside extern "C"
+ * is additive. All pointers are DEVICE pointers on the current device unless stated otherwise.
+ * Nothing here synchronises the device; work is queued on the given stream (the legacy entry point
+ * uses the default stream, as the reference does).
+ *
+ * Operand orders
+ *   "reference order": what the reference's kernel and Python packer exchange --
+ *        sign bits  uint8 (k/2, m/8): bit (i & 7) of byte [q][i >> 3] is kept value q of row i
+ *                   (1 = +1, 0 = -1), i.e. a column-major-in-m 1-bit matrix (csrc/kernel.h:13-15)
+ *        metadata   uint16 (m, k/16) in one of two shuffles (ONEBIT_META_*), 4 nibbles per word,
+ *                   nibble = idx0 | idx1 << 2 of the two kept positions of a group of 4
+ *   "tile order": this library's own streaming order (one 1 KiB sign block and one 2 KiB metadata
+ *        block per 128 x 128 tile; see onebit_packed_*_bytes). Produced by onebit_relayout or
+ *        onebit_pack_from_dense, consumed by onebit_matmul_packed. Needs m % 128 == 0, k % 128 == 0.
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+/* Replaces include/onebit_sparse_tensor.h:5 of the reference (defined in csrc/kernel_lib.cu:23-97),
+ * same symbol (_Z20onebit_sparse_matmulPvS_S_S_S_iii):
+ *   a  sign bits, reference order          b  fp16 (k, n)
+ *   c  ignored (beta = 0; may alias d)     d  fp32 (m, n) output
+ *   e  metadata, ONEBIT_META_CUTLASS order (what the reference kernel's E operand is)
+ * Runs on the default stream. Where the reference prints and exit()s on error, this records the
+ * error for onebit_last_error() and returns without launching. */
+#ifdef __cplusplus
+void onebit_sparse_matmul(void *a, void *b, void *c, void *d, void *e, int m, int n, int k);
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { ONEBIT_META_PYTHON = 0,   /* onebit_sparse_mul/_semi_structured_conversions.py:21-48 */
+       ONEBIT_META_CUTLASS = 1 };/* CUTLASS reorder_meta + ColumnMajorInterleaved<2> (csrc/threadblock.h:198-199) */
+enum { ONEBIT_OUT_F32 = 0, ONEBIT_OUT_F16 = 1 };
+enum { ONEBIT_DENSE_F16 = 0, ONEBIT_DENSE_BF16 = 1, ONEBIT_DENSE_I32 = 2 };
+enum { ONEBIT_KERNEL_AUTO = 0,    /* decode kernel for n <= 16 or n % 8 != 0, tensor-memory kernel otherwise */
+       ONEBIT_KERNEL_PREFILL = 1, /* TMA + tcgen05.mma.sp kernel */
+       ONEBIT_KERNEL_DECODE = 2 };/* split-K cluster kernel for few tokens */
+
+enum { ONEBIT_OK = 0, ONEBIT_ERR_SHAPE = 1, ONEBIT_ERR_NULL = 2, ONEBIT_ERR_CUDA = 3,
+       ONEBIT_ERR_WORKSPACE = 4, ONEBIT_ERR_ARG = 5, ONEBIT_ERR_DEVICE_WAIT = 6 };
+
+/* Message of the calling thread's most recent failed call ("" if none). Host pointer, valid until
+ * the thread's next failing call. Replaces the reference's exit(EXIT_FAILURE) (csrc/kernel_lib.cu:11-20). */
+const char *onebit_last_error(void);
+
+/* Bytes of the tile-ordered operands of an m x k matrix (m, k multiples of 128):
+ * m*k/16 and m*k/8. */
+size_t onebit_packed_bits_bytes(int64_t m, int64_t k);
+size_t onebit_packed_meta_bytes(int64_t m, int64_t k);
+/* Scratch bytes onebit_sparse_matmul_ex needs for a call of this shape (the two above, each
+ * rounded up to 256). */
+size_t onebit_workspace_bytes(int64_t m, int64_t k);
+
+/* Stateless GEMM on reference-ordered operands: the generalisation of onebit_sparse_matmul
+ * (csrc/kernel_lib.cu:23-97) by a per-row scale (NULL = none), an fp16 output, a choice of metadata
+ * order and a stream. Internally: relayout into `workspace`, then the dispatched kernel.
+ * workspace == NULL makes the library use (and grow on demand) a per-device cached allocation,
+ * which serialises concurrent calls on one device. Shapes the tiled kernels do not take
+ * (m % 128, k % 128 != 0; needs m % 32 == 0 (64 for ONEBIT_META_PYTHON), k % 32 == 0) run on a plain
+ * CUDA-core kernel without workspace. stream is a cudaStream_t. */
+int onebit_sparse_matmul_ex(const void *a_bits, const void *b, void *d, const void *e_meta, const void *scale,
+                            int64_t m, int64_t n, int64_t k, int out_type, int meta_dialect,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+/* Reference order -> tile order; the once-per-weight half of onebit_sparse_matmul_ex. It is the
+ * device-side counterpart of handing pack()'s tensors (onebit_sparse_mul/__init__.py:130-145) to
+ * the kernel. */
+int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, int64_t m, int64_t k,
+                    void *bits_tile, void *meta_tile, void *stream);
+
+/* GEMM on tile-ordered operands (the fast path; the hot loop of BinaryLinear_2_4.forward,
+ * onebit_sparse_mul/__init__.py:118-128). kernel: ONEBIT_KERNEL_*. */
+int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
+                         int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
+
+/* Dense (m, k) row-major weights -> packed operands in one pass; bit-exact replacement of
+ * sparse_semi_structured_from_dense_cutlass + binary_quant + .T + pack_binary
+ * (_semi_structured_conversions.py:54-179, onebit_sparse_mul/__init__.py:22-34,139-143).
+ * Every output pointer may be NULL (not produced):
+ *   sparse     (m, k/2) kept values, dense dtype     a_bits   sign bits, reference order
+ *   e_meta     metadata in meta_dialect order        bits_tile / meta_tile   tile order
+ * The input is expected to be 2:4 already; other groups follow the reference's encoder table
+ * (_semi_structured_conversions.py:99-124). Needs k % 32 == 0 and m % 32 == 0 (m % 64 == 0 for
+ * ONEBIT_META_PYTHON, as the reference's scatter does); tile outputs need m, k % 128 == 0. */
+int onebit_pack_from_dense(const void *dense, int dense_dtype, int64_t m, int64_t k, void *sparse,
+                           void *a_bits, void *e_meta, int meta_dialect, void *bits_tile, void *meta_tile,
+                           void *stream);
+
+/* Magnitude 2:4 mask of fp16 weights (mask_creator, _semi_structured_conversions.py:286-314): in
+ * every group of 4 the two smallest |w| are dropped; among equal magnitudes the lower index is
+ * dropped first. masked (fp16, same shape) and mask (uint8 0/1) may each be NULL. count % 8 == 0. */
+int onebit_mask24(const void *dense_f16, int64_t count, void *masked_f16, void *mask_u8, void *stream);
+
+/* Tile order -> dense fp16 (m, k) holding {-1, 0, +1} * scale (scale NULL = 1): the inverse of the
+ * pack (sparse_semi_structured_to_dense_cutlass + dequant_desparse_tile,
+ * _semi_structured_conversions.py:186-283, onebit_sparse_mul/__init__.py:47-65). */
+int onebit_unpack_to_dense(const void *bits_tile, const void *meta_tile, const void *scale, int64_t m, int64_t k,
+                           void *dense_f16, void *stream);
+
+/* Synchronises the current device, then reads and clears its status word: ONEBIT_ERR_DEVICE_WAIT if
+ * a bounded wait inside the tensor-memory kernel gave up since the last call (the kernel then still
+ * terminated, with an unusable result), ONEBIT_OK otherwise. The reference has no counterpart; its
+ * kernel has no device-side waits on other agents. */
+int onebit_check_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,240 @@
+"""B200-native one-bit 2:4 sparse GEMM: host-side mirror of the reference's Python package.
+
+Same names, argument meaning and error behaviour as ``onebit_sparse_mul/__init__.py`` of the
+reference (lines cited per function); underneath, every step is a hand-written sm_100a kernel reached
+through the C ABI of ``libonebitmul.so``. torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from ._lib import (DENSE_BF16, DENSE_F16, DENSE_I32, KERNEL_AUTO, KERNEL_DECODE, KERNEL_PREFILL, META_CUTLASS,
+                   META_PYTHON, OUT_F16, OUT_F32, OneBitError)
+from ._semi_structured_conversions import (mask_creator, sparse_semi_structured_from_dense_cutlass,
+                                           sparse_semi_structured_to_dense_cutlass)
+
+__all__ = [
+    "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
+    "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
+    "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
+    "relayout", "OneBitError",
+]
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(t: torch.Tensor) -> torch.Tensor:
+    if not torch.cuda.is_available():
+        raise OneBitError("no CUDA device: this library has no CPU path")
+    return t if t.is_cuda else t.cuda()
+
+
+def _out_code(dtype) -> int:
+    if dtype == torch.float32:
+        return OUT_F32
+    if dtype == torch.float16:
+        return OUT_F16
+    raise TypeError(f"C must be float32 or float16, got {dtype}")
+
+
+def _dense_code(dtype) -> int:
+    try:
+        return {torch.float16: DENSE_F16, torch.bfloat16: DENSE_BF16, torch.int32: DENSE_I32}[dtype]
+    except KeyError:
+        raise RuntimeError(f"Invalid datatype {dtype} of dense matrix") from None
+
+
+# ---- the GEMM entry points (reference: __init__.py:12-19) ------------------------------------------
+
+def cuda_binary_mul_(A, B, C, meta, scale=None):
+    """C[m, n] = A_sparse @ B, in place into C (reference ``cuda_binary_mul_``, __init__.py:17-19).
+
+    A: uint8 (k/2, m/8) sign bitfield as ``BinaryLinear_2_4.pack`` produces; B: fp16 (k, n);
+    meta: int16 (m, k/16) in the reference packer's order; C: fp32 or fp16 (m, n) on B's device.
+    ``scale`` (fp16 (m,), optional) multiplies output rows.
+    """
+    lib = _lib.load()
+    A, B, meta = _cuda(A), _cuda(B), _cuda(meta)
+    if B.dtype != torch.float16 or A.dtype != torch.uint8 or meta.dtype != torch.int16:
+        raise TypeError("expected A uint8, B float16, meta int16")
+    if not C.is_cuda:
+        raise OneBitError("C must live on the CUDA device")
+    m, k, n = meta.shape[0], B.shape[0], B.shape[1]
+    if A.numel() * 16 != m * k or meta.shape[1] * 16 != k or tuple(C.shape) != (m, n):
+        raise ValueError(f"shape mismatch: A {tuple(A.shape)}, B {tuple(B.shape)}, meta {tuple(meta.shape)}, C {tuple(C.shape)}")
+    A, B, meta = A.contiguous(), B.contiguous(), meta.contiguous()
+    if not C.is_contiguous():
+        raise ValueError("C must be contiguous")
+    if scale is not None:
+        scale = _cuda(scale).to(torch.float16).contiguous()
+    with torch.cuda.device(B.device):
+        need = lib.onebit_workspace_bytes(m, k) if (m % 128 == 0 and k % 128 == 0) else 0
+        ws = torch.empty(max(need, 1), dtype=torch.uint8, device=B.device)
+        _lib.check(lib.onebit_sparse_matmul_ex(_ptr(A), _ptr(B), _ptr(C), _ptr(meta), _ptr(scale), m, n, k,
+                                               _out_code(C.dtype), META_PYTHON, _ptr(ws), ws.numel(), _stream()))
+    return C
+
+
+def cuda_binary_mul(A, B, meta, scale=None, out_dtype=torch.float32):
+    """Allocates C on B's device and returns it (reference ``cuda_binary_mul``, __init__.py:12-15)."""
+    B = _cuda(B)
+    C = torch.empty((meta.shape[0], B.shape[1]), dtype=out_dtype, device=B.device)
+    return cuda_binary_mul_(A, B, C, meta, scale=scale)
+
+
+# ---- pack helpers (reference: __init__.py:22-65) -----------------------------------------------------
+
+def binary_quant(tensor):
+    """1 where tensor > 0 else 0 (reference __init__.py:22-23)."""
+    return torch.where(tensor > 0, torch.tensor(1, device=tensor.device), torch.tensor(0, device=tensor.device))
+
+
+def pack_binary(tensor):
+    """Pack 0/1 values 8 per byte, LSB first, along the last dim (reference __init__.py:25-34)."""
+    shape = list(tensor.shape)
+    shape[-1] = shape[-1] // 8
+    t = tensor.reshape(*shape, 8).to(torch.uint8)
+    weights = (1 << torch.arange(8, device=tensor.device, dtype=torch.int32)).to(torch.uint8)
+    return (t * weights).sum(dim=-1).to(torch.uint8)
+
+
+def unpack_binary(packed_tensor):
+    """Inverse of pack_binary (reference __init__.py:36-45, there a Python double loop)."""
+    shifts = torch.arange(8, device=packed_tensor.device, dtype=torch.uint8)
+    bits = (packed_tensor.unsqueeze(-1) >> shifts) & 1
+    return bits.reshape(*packed_tensor.shape[:-1], packed_tensor.shape[-1] * 8)
+
+
+def dequant_desparse_tile(packed_sparse_tile, meta_tile):
+    """(rows, k/16) un-transposed sign bytes + reference-ordered meta -> dense {-1,0,+1} (rows, k)
+    (reference __init__.py:47-65)."""
+    sparse_tile = unpack_binary(packed_sparse_tile)
+    sparse_tile = torch.where(sparse_tile == 1, 1, -1).to(torch.int32)
+    return sparse_semi_structured_to_dense_cutlass(sparse_tile, meta_tile)
+
+
+def py_binary_gemm(x, packed_sparse_tensor, sparse_meta):
+    """x (t, rows) @ dequant(V) (rows, cols): the reference's check product (__init__.py:67-97).
+    Kept for API parity; it is a validation helper, not the hot path."""
+    if packed_sparse_tensor.dtype != torch.uint8:
+        raise ValueError("packed_sparse_tensor must be `torch.uint8`")
+    if packed_sparse_tensor.shape[0] != x.shape[1]:
+        raise ValueError("x.shape[1] must equal to packed_sparse_tensor.shape[0], so we can matmul(x, packed_sparse_tensor)")
+    if sparse_meta.dtype != torch.int16:
+        raise ValueError("Sparse Meta must be `torch.int16`")
+    dense_tile = dequant_desparse_tile(packed_sparse_tensor, sparse_meta)
+    return torch.matmul(x, dense_tile.to(torch.float16).to(x.device))
+
+
+# ---- tile-ordered weights: the fast path ---------------------------------------------------------------
+
+class PackedWeight:
+    """A weight matrix in this library's streaming order plus its reference-ordered twin."""
+
+    def __init__(self, m, k, bits_tile, meta_tile, scale=None, packed_binary_sparse=None, meta=None):
+        self.m, self.k = m, k
+        self.bits_tile, self.meta_tile, self.scale = bits_tile, meta_tile, scale
+        self.packed_binary_sparse, self.meta = packed_binary_sparse, meta
+
+
+def pack_weight(weight, scale=None, apply_mask=True, keep_reference=True, meta_dialect=META_PYTHON) -> PackedWeight:
+    """Dense (m, k) fp16/bf16/int32 weights -> PackedWeight, entirely on the GPU: 2:4 magnitude mask
+    (fp16 only; skip with apply_mask=False when the weights are 2:4 already), compress, encode,
+    quantise, bit-pack (the body of reference ``BinaryLinear_2_4.pack``, __init__.py:130-145)."""
+    lib = _lib.load()
+    w = _cuda(weight).contiguous()
+    m, k = w.shape
+    dev = w.device
+    with torch.cuda.device(dev):
+        if apply_mask:
+            if w.dtype != torch.float16:
+                raise TypeError("the GPU mask kernel takes float16 weights; pass apply_mask=False for pre-masked input")
+            masked = torch.empty_like(w)
+            _lib.check(lib.onebit_mask24(_ptr(w), w.numel(), _ptr(masked), None, _stream()))
+            w = masked
+        tiled = m % 128 == 0 and k % 128 == 0
+        bits_tile = torch.empty(m * k // 16, dtype=torch.uint8, device=dev) if tiled else None
+        meta_tile = torch.empty(m * k // 8, dtype=torch.uint8, device=dev) if tiled else None
+        a_bits = torch.empty((k // 2, m // 8), dtype=torch.uint8, device=dev) if keep_reference else None
+        e_meta = torch.empty((m, k // 16), dtype=torch.int16, device=dev) if keep_reference else None
+        _lib.check(lib.onebit_pack_from_dense(_ptr(w), _dense_code(w.dtype), m, k, None, _ptr(a_bits), _ptr(e_meta),
+                                              meta_dialect, _ptr(bits_tile), _ptr(meta_tile), _stream()))
+    if scale is not None:
+        scale = _cuda(scale).to(torch.float16).contiguous()
+    return PackedWeight(m, k, bits_tile, meta_tile, scale, a_bits, e_meta)
+
+
+def relayout(packed_binary_sparse, meta, meta_dialect=META_PYTHON, scale=None) -> PackedWeight:
+    """Reference-ordered operands (what the reference's pack() stores) -> PackedWeight."""
+    lib = _lib.load()
+    A, meta = _cuda(packed_binary_sparse).contiguous(), _cuda(meta).contiguous()
+    m, k = meta.shape[0], meta.shape[1] * 16
+    with torch.cuda.device(A.device):
+        bits_tile = torch.empty(m * k // 16, dtype=torch.uint8, device=A.device)
+        meta_tile = torch.empty(m * k // 8, dtype=torch.uint8, device=A.device)
+        _lib.check(lib.onebit_relayout(_ptr(A), _ptr(meta), meta_dialect, m, k, _ptr(bits_tile), _ptr(meta_tile), _stream()))
+    if scale is not None:
+        scale = _cuda(scale).to(torch.float16).contiguous()
+    return PackedWeight(m, k, bits_tile, meta_tile, scale, A, meta)
+
+
+def matmul_packed(pw: PackedWeight, B, out=None, out_dtype=torch.float32, kernel=KERNEL_AUTO):
+    """C (m, n) = pw @ B for B fp16 (k, n) on the weight's device."""
+    lib = _lib.load()
+    if not B.is_cuda or B.dtype != torch.float16 or B.shape[0] != pw.k:
+        raise ValueError("B must be a CUDA float16 tensor of shape (k, n)")
+    B = B.contiguous()
+    n = B.shape[1]
+    if out is None:
+        out = torch.empty((pw.m, n), dtype=out_dtype, device=B.device)
+    with torch.cuda.device(B.device):
+        _lib.check(lib.onebit_matmul_packed(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(B), _ptr(out),
+                                            pw.m, n, pw.k, _out_code(out.dtype), kernel, _stream()))
+    return out
+
+
+# ---- the module (reference: __init__.py:101-145) ----------------------------------------------------------
+
+class BinaryLinear_2_4(nn.Module):
+    """1-bit 2:4 sparse linear layer without bias (reference ``BinaryLinear_2_4``).
+
+    Same attributes as the reference (``packed_binary_sparse`` uint8 (in/2, out/8), ``meta`` int16
+    (out, in/16), ``vaild``), here registered as buffers together with the tile-ordered operands the
+    kernels read, so that ``state_dict`` and ``.to()`` carry them. ``forward(x)`` takes x as the
+    kernel does, (in, tokens), and returns (out, tokens).
+    """
+
+    def __init__(self, infeatures: int, outfeatures: int, out_dtype=torch.float32):
+        super().__init__()
+        if infeatures % 128 != 0 or outfeatures % 128 != 0:
+            raise ValueError("`infeatures` and `outfeatures` must be divisible by 128.")
+        self.infeatures, self.outfeatures, self.out_dtype = infeatures, outfeatures, out_dtype
+        self.register_buffer("packed_binary_sparse", torch.zeros((infeatures // 2, outfeatures // 8), dtype=torch.uint8))
+        self.register_buffer("meta", torch.zeros((outfeatures, infeatures // 16), dtype=torch.int16))
+        self.register_buffer("bits_tile", torch.zeros(outfeatures * infeatures // 16, dtype=torch.uint8))
+        self.register_buffer("meta_tile", torch.zeros(outfeatures * infeatures // 8, dtype=torch.uint8))
+        self.register_buffer("scale", None)
+        self.vaild = False
+
+    def forward(self, x):
+        if not self.vaild:
+            raise NotImplementedError("the BinaryLinear")
+        pw = PackedWeight(self.outfeatures, self.infeatures, self.bits_tile, self.meta_tile, self.scale)
+        return matmul_packed(pw, x, out_dtype=self.out_dtype)
+
+    def pack(self, weight, scale=None):
+        """weight: (outfeatures, infeatures). Mask to 2:4 by magnitude, compress, quantise, pack."""
+        if tuple(weight.shape) != (self.outfeatures, self.infeatures):
+            raise ValueError(f"weight must be ({self.outfeatures}, {self.infeatures})")
+        pw = pack_weight(weight.to(torch.float16) if weight.dtype == torch.float32 else weight, scale=scale)
+        self.packed_binary_sparse, self.meta = pw.packed_binary_sparse, pw.meta
+        self.bits_tile, self.meta_tile, self.scale = pw.bits_tile, pw.meta_tile, pw.scale
+        self.vaild = True

@@ -1,0 +1,235 @@
+// The C ABI of libonebitmul (declared in include/onebit_sparse_tensor.h) and the host dispatcher.
+//
+// Counterpart of the reference's csrc/kernel_lib.cu:23-97: where that file wraps the pointers into
+// CUTLASS TensorRefs and launches one templated SparseGemm, this one validates the shape, brings
+// reference-ordered operands into tile order (relayout.cu) and picks one of two hand-written
+// kernels by shape: the split-K cluster kernel for few tokens (gemm_decode.cu) or the TMA +
+// tcgen05.mma.sp kernel (gemm_prefill_sm100.cu). There is no CPU path: without a CUDA device every
+// entry point fails with ONEBIT_ERR_CUDA.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/onebit_sparse_tensor.h"
+#include "formats.h"
+#include "kernels.h"
+
+static_assert(ONEBIT_META_PYTHON == OB_META_PYTHON && ONEBIT_META_CUTLASS == OB_META_CUTLASS, "enum drift");
+static_assert(ONEBIT_OUT_F32 == OB_OUT_F32 && ONEBIT_OUT_F16 == OB_OUT_F16, "enum drift");
+static_assert(ONEBIT_DENSE_F16 == OB_DENSE_F16 && ONEBIT_DENSE_BF16 == OB_DENSE_BF16 && ONEBIT_DENSE_I32 == OB_DENSE_I32, "enum drift");
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(ONEBIT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
+
+bool tiled_shape(int64_t m, int64_t k) { return m > 0 && k > 0 && m % OB_TILE_M == 0 && k % OB_TILE_K == 0; }
+
+// Per-device scratch owned by the library: the relayout target of the stateless entry points and
+// the status word of the tensor-memory kernel. Grown on demand, never shrunk, freed at process
+// exit by the driver.
+struct DeviceScratch {
+  void* buf = nullptr;
+  size_t bytes = 0;
+  int* status = nullptr;
+};
+std::mutex g_mu;
+DeviceScratch g_scratch[64];
+
+int get_status_word(int** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceScratch& s = g_scratch[dev];
+  if (!s.status) {
+    e = cudaMalloc(&s.status, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
+    e = cudaMemset(s.status, 0, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
+  }
+  *out = s.status;
+  return ONEBIT_OK;
+}
+
+int get_scratch(size_t bytes, void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceScratch& s = g_scratch[dev];
+  if (s.bytes < bytes) {
+    if (s.buf) {
+      // earlier launches may still read the old buffer
+      e = cudaDeviceSynchronize();
+      if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+      cudaFree(s.buf);
+      s.buf = nullptr;
+      s.bytes = 0;
+    }
+    e = cudaMalloc(&s.buf, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(scratch)");
+    s.bytes = bytes;
+  }
+  *out = s.buf;
+  return ONEBIT_OK;
+}
+
+int check_dialect_rows(int dialect, int64_t m) {
+  if (dialect != OB_META_PYTHON && dialect != OB_META_CUTLASS) return fail(ONEBIT_ERR_ARG, "unknown metadata order %d", dialect);
+  if (m % ob_meta_row_granule(dialect) != 0)
+    return fail(ONEBIT_ERR_SHAPE, "m = %lld must be a multiple of %d for this metadata order", (long long)m,
+                ob_meta_row_granule(dialect));
+  return ONEBIT_OK;
+}
+
+int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
+                       int64_t m, int64_t n, int64_t k, int out_type, int kernel, cudaStream_t stream) {
+  if (!bits_tile || !meta_tile || !b || !d) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (!tiled_shape(m, k) || n < 1)
+    return fail(ONEBIT_ERR_SHAPE, "tile-ordered GEMM needs m %% 128 == 0, k %% 128 == 0, n >= 1 (got m=%lld n=%lld k=%lld)",
+                (long long)m, (long long)n, (long long)k);
+  if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type %d", out_type);
+  if (kernel == ONEBIT_KERNEL_AUTO)
+    kernel = (n > 16 && ob::prefill_supported(m, n, k)) ? ONEBIT_KERNEL_PREFILL : ONEBIT_KERNEL_DECODE;
+  cudaError_t e;
+  if (kernel == ONEBIT_KERNEL_PREFILL) {
+    if (!ob::prefill_supported(m, n, k))
+      return fail(ONEBIT_ERR_SHAPE, "the tensor-memory kernel needs n %% 8 == 0 (got n=%lld)", (long long)n);
+    int* status = nullptr;
+    if (int rc = get_status_word(&status)) return rc;
+    e = ob::launch_gemm_prefill(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, status, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "tensor-memory GEMM launch");
+  } else if (kernel == ONEBIT_KERNEL_DECODE) {
+    e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "decode GEMM launch");
+  } else {
+    return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
+  }
+  return ONEBIT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* onebit_last_error(void) { return g_err; }
+
+size_t onebit_packed_bits_bytes(int64_t m, int64_t k) { return (size_t)(m * k / 16); }
+size_t onebit_packed_meta_bytes(int64_t m, int64_t k) { return (size_t)(m * k / 8); }
+size_t onebit_workspace_bytes(int64_t m, int64_t k) {
+  return round256(onebit_packed_bits_bytes(m, k)) + round256(onebit_packed_meta_bytes(m, k));
+}
+
+int onebit_relayout(const void* a_bits, const void* e_meta, int meta_dialect, int64_t m, int64_t k, void* bits_tile,
+                    void* meta_tile, void* stream) {
+  if (!a_bits || !e_meta || !bits_tile || !meta_tile) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (!tiled_shape(m, k)) return fail(ONEBIT_ERR_SHAPE, "tile order needs m %% 128 == 0 and k %% 128 == 0 (got m=%lld k=%lld)", (long long)m, (long long)k);
+  if (int rc = check_dialect_rows(meta_dialect, m)) return rc;
+  cudaError_t e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "relayout launch");
+}
+
+int onebit_matmul_packed(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
+                         int64_t m, int64_t n, int64_t k, int out_type, int kernel, void* stream) {
+  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, static_cast<cudaStream_t>(stream));
+}
+
+int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const void* e_meta, const void* scale, int64_t m,
+                            int64_t n, int64_t k, int out_type, int meta_dialect, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  if (!a_bits || !b || !d || !e_meta) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (m <= 0 || n <= 0 || k <= 0 || k % 32 != 0)
+    return fail(ONEBIT_ERR_SHAPE, "need m, n > 0 and k %% 32 == 0 (got m=%lld n=%lld k=%lld)", (long long)m, (long long)n, (long long)k);
+  if (int rc = check_dialect_rows(meta_dialect, m)) return rc;
+  if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type %d", out_type);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (!tiled_shape(m, k)) {
+    cudaError_t e = ob::launch_gemm_simple(a_bits, e_meta, meta_dialect, scale, b, d, m, n, k, out_type, st);
+    return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "plain GEMM launch");
+  }
+  const size_t need = onebit_workspace_bytes(m, k);
+  if (workspace) {
+    if (workspace_bytes < need) return fail(ONEBIT_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(ONEBIT_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  } else {
+    if (int rc = get_scratch(need, &workspace)) return rc;
+  }
+  void* bits_tile = workspace;
+  void* meta_tile = static_cast<char*>(workspace) + round256(onebit_packed_bits_bytes(m, k));
+  cudaError_t e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
+  if (e != cudaSuccess) return cuda_fail(e, "relayout launch");
+  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, st);
+}
+
+int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits,
+                           void* e_meta, int meta_dialect, void* bits_tile, void* meta_tile, void* stream) {
+  if (!dense) return fail(ONEBIT_ERR_NULL, "null dense pointer");
+  if (dense_dtype < OB_DENSE_F16 || dense_dtype > OB_DENSE_I32) return fail(ONEBIT_ERR_ARG, "unknown dense dtype %d", dense_dtype);
+  if (m <= 0 || k <= 0 || k % 32 != 0 || m % 32 != 0)
+    return fail(ONEBIT_ERR_SHAPE, "need m %% 32 == 0 and k %% 32 == 0 (got m=%lld k=%lld)", (long long)m, (long long)k);
+  if (e_meta) { if (int rc = check_dialect_rows(meta_dialect, m)) return rc; }
+  if ((bits_tile || meta_tile) && !tiled_shape(m, k))
+    return fail(ONEBIT_ERR_SHAPE, "tile order needs m %% 128 == 0 and k %% 128 == 0 (got m=%lld k=%lld)", (long long)m, (long long)k);
+  cudaError_t e = ob::launch_pack(dense, dense_dtype, m, k, sparse, a_bits, e_meta, meta_dialect, bits_tile, meta_tile,
+                                  static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "pack launch");
+}
+
+int onebit_mask24(const void* dense_f16, int64_t count, void* masked_f16, void* mask_u8, void* stream) {
+  if (!dense_f16) return fail(ONEBIT_ERR_NULL, "null dense pointer");
+  if (count < 0 || count % 8 != 0) return fail(ONEBIT_ERR_SHAPE, "element count %lld must be a multiple of 8", (long long)count);
+  cudaError_t e = ob::launch_mask24(dense_f16, count, masked_f16, mask_u8, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "mask launch");
+}
+
+int onebit_unpack_to_dense(const void* bits_tile, const void* meta_tile, const void* scale, int64_t m, int64_t k,
+                           void* dense_f16, void* stream) {
+  if (!bits_tile || !meta_tile || !dense_f16) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (!tiled_shape(m, k)) return fail(ONEBIT_ERR_SHAPE, "tile order needs m %% 128 == 0 and k %% 128 == 0");
+  cudaError_t e = ob::launch_tile_to_dense(bits_tile, meta_tile, scale, m, k, dense_f16, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "unpack launch");
+}
+
+// Reads and clears the status word of the tensor-memory kernel on the current device. Synchronises
+// the device. Returns ONEBIT_ERR_DEVICE_WAIT if a bounded wait inside a kernel gave up since the
+// last call.
+int onebit_check_device_status(void) {
+  int* status = nullptr;
+  if (int rc = get_status_word(&status)) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+  int host = 0;
+  e = cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
+  if (host != 0) {
+    cudaMemset(status, 0, sizeof(int));
+    return fail(ONEBIT_ERR_DEVICE_WAIT, "a bounded wait inside the tensor-memory kernel gave up (role code %d)", host);
+  }
+  return ONEBIT_OK;
+}
+
+}  // extern "C"
+
+// The reference's entry point, same C++-mangled symbol (include/onebit_sparse_tensor.h:5 and
+// csrc/kernel_lib.cu:23 of the reference).
+void onebit_sparse_matmul(void* a, void* b, void* /*c*/, void* d, void* e, int m, int n, int k) {
+  onebit_sparse_matmul_ex(a, b, d, e, nullptr, m, n, k, ONEBIT_OUT_F32, ONEBIT_META_CUTLASS, nullptr, 0, nullptr);
+}

@@ -1,0 +1,371 @@
+// K2: the compute-bound kernel (prefill / square shapes) on the 5th-generation tensor cores.
+//
+// Replaces the reference's CUTLASS SparseGemm instantiation (csrc/kernel.h:13-72, threadblock.h,
+// warp.h: cp.async multistage + warp-level mma.sp m16n8k32) with a hand-written sm_100a kernel:
+//
+//   producer warp   TMA: the fp16 token tile B (k x n row-major, 128-byte swizzle) through a tensor
+//                   map, and the tile-ordered sign bits (1 KiB) and metadata (2 KiB) of the
+//                   128x128 weight tile as plain bulk copies; one mbarrier transaction per stage
+//   expander warps  thread = weight row: 64 sign bits -> 64 exact fp16 +-1 values (one shift and
+//                   one logic op per pair), written K-major with the 128-byte swizzle
+//   MMA thread      tcgen05.cp moves the metadata block into 4 tensor-memory columns, then
+//                   4 x tcgen05.mma.sp.kind::f16 (M=128, N=BN, K=32 dense) per stage, fp32
+//                   accumulators in tensor memory; tcgen05.commit frees the stage
+//   epilogue warps  tcgen05.ld -> per-row scale -> fp16 / fp32 -> 16-byte global stores
+//
+// Every wait on an mbarrier is bounded: after ~1 s a thread records a code in the status word and
+// carries on without waiting, so the kernel always terminates and releases its tensor memory.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "formats.h"
+#include "kernels.h"
+
+namespace {
+
+constexpr int BM = 128;             // weight rows per CTA
+constexpr int BK = 128;             // dense k per stage = one weight tile
+constexpr int kNumThreads = 320;    // warp 0 producer, 1 MMA, 2-5 expander, 6-9 epilogue
+
+template <int BN> struct Cfg {
+  static constexpr int kABytes = BM * 128;                 // 128 rows x 64 fp16
+  static constexpr int kBBoxBytes = BK * 128;              // 128 k-rows x 64 tokens x 2 B
+  static constexpr int kBBytes = (BN / 64) * kBBoxBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
+  static constexpr int kStages = (BN == 128) ? 4 : 2;
+  static constexpr int kTxBytes = kBBytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
+  static constexpr int kTmemCols = (BN == 128) ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+};
+
+struct PrefillArgs {
+  const uint8_t* bits_tile;
+  const uint8_t* meta_tile;
+  const __half* scale;
+  void* d;
+  int64_t m, n, k;
+  int out_type;
+  int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait. `budget_ns` is this thread's remaining patience; once a wait has run out the
+// thread stops waiting for anything (budget 0), records `code` and lets the kernel drain.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint64_t& budget_ns, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  if (budget_ns == 0) return;
+  const uint64_t start = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (globaltimer_ns() - start > budget_ns) {
+      budget_ns = 0;
+      atomicCAS(status, 0, code);
+      return;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_sp_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem,
+                                                   uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptors (sm_100 format: version 1 at bit 46, layout type at bits 61-63)
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2;
+
+__device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
+  return ((w << (15 - j)) & 0x80008000u) ^ 0xBC00BC00u;
+}
+
+// ---- the kernel -------------------------------------------------------------------------------
+
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  // stage s: [A 16 KiB][B BN/64 x 16 KiB][meta 2 KiB][bits 1 KiB]
+  auto stage_a = [&](int s) { return smem_base + s * C::kStageBytes; };
+  auto stage_b = [&](int s) { return stage_a(s) + C::kABytes; };
+  auto stage_e = [&](int s) { return stage_b(s) + C::kBBytes; };
+  auto stage_bits = [&](int s) { return stage_e(s) + OB_TILE_META_BYTES; };
+  const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
+  auto bar_full = [&](int s) { return bar_base + 8 * s; };                       // TMA landed
+  auto bar_afull = [&](int s) { return bar_base + 8 * (C::kStages + s); };       // +-1 values written
+  auto bar_empty = [&](int s) { return bar_base + 8 * (2 * C::kStages + s); };   // MMAs of the stage done
+  const uint32_t bar_acc = bar_base + 8 * (3 * C::kStages);
+  const uint32_t tmem_slot = bar_acc + 8;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t mb = blockIdx.x;
+  const int64_t n0 = (int64_t)blockIdx.y * BN;
+  const int kt = (int)(a.k / BK);
+  uint64_t budget = 1000000000ull;   // ns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_afull(s), 128); mbar_init(bar_empty(s), 1); }
+    mbar_init(bar_acc, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+  }
+  if (warp == 1) tcgen05_alloc(tmem_slot, C::kTmemCols);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+  const uint32_t tmem_acc = tmem_base;                 // columns [0, BN)
+  const uint32_t tmem_e = tmem_base + BN;              // two 4-column metadata slots
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const uint8_t* meta_src = a.meta_tile + (mb * kt) * (int64_t)OB_TILE_META_BYTES;
+      const uint8_t* bits_src = a.bits_tile + (mb * kt) * (int64_t)OB_TILE_BITS_BYTES;
+      for (int it = 0; it < kt; ++it) {
+        const int s = it % C::kStages;
+        mbar_wait(bar_empty(s), ((it / C::kStages) & 1) ^ 1, budget, a.status, 1);
+        mbar_expect_tx(bar_full(s), C::kTxBytes);
+#pragma unroll
+        for (int j = 0; j < BN / 64; ++j)
+          tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * BK, bar_full(s));
+        bulk_load(stage_e(s), meta_src + (int64_t)it * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
+        bulk_load(stage_bits(s), bits_src + (int64_t)it * OB_TILE_BITS_BYTES, OB_TILE_BITS_BYTES, bar_full(s));
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 2) /*sparse*/ | (1u << 4) /*fp32 accumulate*/ | (1u << 16) /*B is n-major*/ |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      for (int it = 0; it < kt; ++it) {
+        const int s = it % C::kStages;
+        const uint32_t ph = (it / C::kStages) & 1;
+        mbar_wait(bar_full(s), ph, budget, a.status, 2);
+        mbar_wait(bar_afull(s), ph, budget, a.status, 3);
+        tcgen05_fence_after();
+        const uint32_t e_col = tmem_e + 4 * (it & 1);
+        tcgen05_cp_128x128b(e_col, make_desc(stage_e(s), 128, 128, kLayoutNone));
+        const uint64_t adesc = make_desc(stage_a(s), 16, 1024, kLayoutSw128);
+        const uint64_t bdesc = make_desc(stage_b(s), C::kBBoxBytes, 1024, kLayoutSw128);
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          // k-block kb: 32 bytes further along the swizzled A rows, 32 k-rows (4 KiB) further in B,
+          // metadata column kb = even column address + id2
+          tcgen05_mma_sp_f16(tmem_acc, adesc + (uint64_t)(2 * kb), bdesc + (uint64_t)(256 * kb),
+                             e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
+        }
+        tcgen05_commit(bar_empty(s));
+      }
+      tcgen05_commit(bar_acc);
+    }
+  } else if (warp < 6) {
+    // ---------------- expander: thread = weight row ----------------
+    const int r = (warp - 2) * 32 + lane;
+    for (int it = 0; it < kt; ++it) {
+      const int s = it % C::kStages;
+      mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 4);
+      const uint2 w = *reinterpret_cast<const uint2*>(smem_gen + (stage_bits(s) - smem_base) + r * 8);
+      uint8_t* arow = smem_gen + (stage_a(s) - smem_base) + r * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t word = (c < 4) ? w.x : w.y;
+        uint4 v;
+        v.x = expand_pair(word, 4 * (c & 3) + 0);
+        v.y = expand_pair(word, 4 * (c & 3) + 1);
+        v.z = expand_pair(word, 4 * (c & 3) + 2);
+        v.w = expand_pair(word, 4 * (c & 3) + 3);
+        *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_arrive(bar_afull(s));
+    }
+  } else {
+    // ---------------- epilogue: warp quadrant = warp % 4, thread = output row ----------------
+    const int q = warp & 3;
+    mbar_wait(bar_acc, 0, budget, a.status, 5);
+    tcgen05_fence_after();
+    const int64_t row = mb * BM + q * 32 + lane;
+    const float sc = a.scale ? __half2float(a.scale[row]) : 1.f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t v[32];
+      tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+      const int64_t col = n0 + c0;
+      if (col >= a.n) continue;
+      if (a.out_type == OB_OUT_F16) {
+        __half* dst = static_cast<__half*>(a.d) + row * a.n + col;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (col + 8 * j < a.n) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
+              ow[h] = *reinterpret_cast<const uint32_t*>(&p);
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+          }
+        }
+      } else {
+        float* dst = static_cast<float*>(a.d) + row * a.n + col;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (col + 4 * j < a.n) {
+            float4 o = make_float4(__uint_as_float(v[4 * j]) * sc, __uint_as_float(v[4 * j + 1]) * sc,
+                                   __uint_as_float(v[4 * j + 2]) * sc, __uint_as_float(v[4 * j + 3]) * sc);
+            *reinterpret_cast<float4*>(dst + 4 * j) = o;
+          }
+        }
+      }
+    }
+    tcgen05_fence_before();
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tcgen05_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+template <int BN>
+cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  dim3 grid((unsigned)(a.m / BM), (unsigned)((a.n + BN - 1) / BN));
+  ob_gemm_prefill_kernel<BN><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+namespace ob {
+
+bool prefill_supported(int64_t m, int64_t n, int64_t k) {
+  return m % BM == 0 && k % BK == 0 && n % 8 == 0 && n >= 8 && k >= BK;
+}
+
+cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                                void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                cudaStream_t stream) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(b) & 15) != 0) return cudaErrorMisalignedAddress;
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)k};
+  const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)BK};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  PrefillArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
+                static_cast<const __half*>(scale), d, m, n, k, out_type, status};
+  return launch<128>(tmap, a, stream);
+}
+
+}  // namespace ob

@@ -1,0 +1,34 @@
+// Launchers of the CUDA kernels behind the C ABI (internal header).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ob {
+
+// K1 (pack.cu)
+cudaError_t launch_pack(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse,
+                        void* bits_ref, void* meta_ref, int dialect, void* bits_tile, void* meta_tile,
+                        cudaStream_t stream);
+// 2:4 magnitude mask (mask.cu)
+cudaError_t launch_mask24(const void* dense_f16, int64_t count, void* masked_f16, void* mask_u8,
+                          cudaStream_t stream);
+// K4 (relayout.cu)
+cudaError_t launch_relayout(const void* bits_ref, const void* meta_ref, int dialect, int64_t m, int64_t k,
+                            void* bits_tile, void* meta_tile, cudaStream_t stream);
+cudaError_t launch_tile_to_dense(const void* bits_tile, const void* meta_tile, const void* scale, int64_t m,
+                                 int64_t k, void* dense, cudaStream_t stream);
+// plain one-thread-per-output kernel on the reference orders (gemm_simple.cu)
+cudaError_t launch_gemm_simple(const void* bits_ref, const void* meta_ref, int dialect, const void* scale,
+                               const void* b, void* d, int64_t m, int64_t n, int64_t k, int out_type,
+                               cudaStream_t stream);
+// K3: decode kernel, n small (gemm_decode.cu). tile-ordered operands.
+cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                               void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream);
+// K2: tcgen05 kernel (gemm_prefill_sm100.cu). tile-ordered operands; n % 8 == 0.
+// status: device word that receives a non-zero code if a bounded wait inside the kernel gave up.
+cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                                void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                cudaStream_t stream);
+bool prefill_supported(int64_t m, int64_t n, int64_t k);
+
+}  // namespace ob

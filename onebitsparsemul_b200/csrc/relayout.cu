@@ -1,0 +1,103 @@
+// K4: reference operand orders -> tile order, and tile order -> dense (the inverse of the pack).
+//
+// The reference hands its kernel a sign bitfield that is column-major in m and a metadata matrix in
+// one of two shuffled orders (csrc/kernel.h:13-18, csrc/threadblock.h:198-199,
+// onebit_sparse_mul/_semi_structured_conversions.py:21-48). The GEMM kernels of this library read
+// 128x128 tiles whose sign bits are row-major in k and whose metadata is laid out for tensor
+// memory. This kernel is the bit transpose between the two; one CTA per tile, HBM-bound
+// (3/16 byte read and written per dense weight).
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "formats.h"
+#include "kernels.h"
+
+namespace {
+
+__global__ void __launch_bounds__(256) ob_relayout_kernel(const uint32_t* __restrict__ bits_ref,
+                                                          const uint16_t* __restrict__ meta_ref, int dialect,
+                                                          int64_t m, int64_t k, uint32_t* __restrict__ bits_tile,
+                                                          uint16_t* __restrict__ meta_tile) {
+  const int64_t kb = blockIdx.x, mb = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t tile = mb * (k / 128) + kb;
+
+  // sign bits: warp = (32-row group, half of the 64 kept values). Lane l fetches the bitfield word
+  // of the kept value whose tile-order bit position is l; ballot j then is tile row j's word.
+  {
+    const int rg = warp & 3, half = warp >> 2;
+    const int q_local = half * 32 + 2 * (lane & 15) + (lane >> 4);
+    const int64_t q = kb * 64 + q_local;
+    const uint32_t w = __ldg(&bits_ref[(q * m + mb * 128 + rg * 32) >> 5]);
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const uint32_t b = __ballot_sync(0xffffffffu, (w >> j) & 1u);
+      if (lane == j) mine = b;
+    }
+    bits_tile[tile * 256 + (rg * 32 + lane) * 2 + half] = mine;
+  }
+  // metadata: gather through the reference order, store in tile order (consecutive threads write
+  // consecutive uint16 of the tile block)
+  for (int i = threadIdx.x; i < 1024; i += 256) {
+    const int u = i >> 3, wd = i & 7;
+    const int r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4, c2 = wd >> 1, r1 = wd & 1;
+    const int64_t row = mb * 128 + r0 + 8 * r1 + 16 * r2, chunk = kb * 8 + 2 * c2 + c1;
+    meta_tile[tile * 1024 + i] = __ldg(&meta_ref[ob_meta_ref_offset(dialect, m, row, chunk)]);
+  }
+}
+
+// tile order -> dense {-1, 0, +1} * scale, fp16 row-major (m, k). Used by the Python-level
+// inverse (sparse_semi_structured_to_dense_cutlass / dequant_desparse_tile of the reference,
+// _semi_structured_conversions.py:186-283, __init__.py:47-65) and by tests.
+__global__ void __launch_bounds__(256) ob_tile_to_dense_kernel(const uint32_t* __restrict__ bits_tile,
+                                                               const uint16_t* __restrict__ meta_tile,
+                                                               const __half* __restrict__ scale, int64_t m, int64_t k,
+                                                               __half* __restrict__ dense) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one (row, chunk) each
+  const int64_t nchunks = k / 16;
+  if (idx >= m * nchunks) return;
+  const int64_t row = idx / nchunks, chunk = idx % nchunks;
+  const unsigned meta = meta_tile[ob_meta_tile_offset(k, row, chunk)];
+  const float s = scale ? __half2float(scale[row]) : 1.f;
+  __align__(16) __half out[16];
+#pragma unroll
+  for (int t = 0; t < 16; ++t) out[t] = __float2half(0.f);
+#pragma unroll
+  for (int t = 0; t < 8; ++t) {
+    const int e = (meta >> (2 * t)) & 3;
+    const int64_t bi = ob_bits_tile_index(k, row, chunk * 8 + t);
+    const bool plus = (bits_tile[bi >> 5] >> (bi & 31)) & 1u;
+    const __half v = __float2half(plus ? s : -s);
+    const int pos = (t >> 1) * 4 + e;
+#pragma unroll
+    for (int p = 0; p < 16; ++p) if (p == pos) out[p] = v;
+  }
+  uint4* dst = reinterpret_cast<uint4*>(dense + row * k + chunk * 16);
+  dst[0] = reinterpret_cast<uint4*>(out)[0];
+  dst[1] = reinterpret_cast<uint4*>(out)[1];
+}
+
+}  // namespace
+
+namespace ob {
+
+cudaError_t launch_relayout(const void* bits_ref, const void* meta_ref, int dialect, int64_t m, int64_t k,
+                            void* bits_tile, void* meta_tile, cudaStream_t stream) {
+  dim3 grid((unsigned)(k / 128), (unsigned)(m / 128));
+  ob_relayout_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(bits_ref),
+                                               static_cast<const uint16_t*>(meta_ref), dialect, m, k,
+                                               static_cast<uint32_t*>(bits_tile), static_cast<uint16_t*>(meta_tile));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tile_to_dense(const void* bits_tile, const void* meta_tile, const void* scale, int64_t m,
+                                 int64_t k, void* dense, cudaStream_t stream) {
+  const int64_t items = m * (k / 16);
+  ob_tile_to_dense_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint32_t*>(bits_tile), static_cast<const uint16_t*>(meta_tile),
+      static_cast<const __half*>(scale), m, k, static_cast<__half*>(dense));
+  return cudaGetLastError();
+}
+
+}  // namespace ob

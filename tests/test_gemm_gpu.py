@@ -1,0 +1,185 @@
+"""GEMM parity through the C ABI: every kernel against the CPU oracle on the same seeded inputs.
+
+Integer-valued tokens (the reference CLI's fixture, tests/kernel_test.cu:321-332) make every partial
+sum exact, so those cases are compared bit for bit; normally distributed tokens are held to the
+path's stated bound, max |err| <= 1e-2 * |row|_inf on the fp16 output with fp32 accumulation.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from onebitsparsemul_b200 import _lib
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    assert torch.cuda.is_available()
+    return _lib.load()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+class Problem:
+    """Seeded weights in every order the ABI takes, on host and device."""
+
+    def __init__(self, seed, m, k, dialect=_lib.META_PYTHON):
+        rng = np.random.default_rng(seed)
+        self.m, self.k, self.dialect, self.rng = m, k, dialect, rng
+        self.dense, self.scale = helpers.make_weights(rng, m, k)
+        canon, signs, _ = oracle.compress(self.dense)
+        self.a_bits, self.e_meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, dialect)
+        self.d_bits, self.d_meta, self.d_scale = dev(self.a_bits), dev(self.e_meta.view(np.int16)), dev(self.scale)
+        if m % 128 == 0 and k % 128 == 0:
+            bt, mt = helpers.tile_order_from_canonical(canon, signs)
+            self.d_bits_tile, self.d_meta_tile = dev(bt), dev(mt)
+
+    def oracle(self, B, use_scale):
+        return oracle.gemm(self.a_bits, self.e_meta, self.dialect, B, self.m, scale=self.scale if use_scale else None)
+
+
+def run_packed(lib, p, B, out_dtype, kernel, use_scale):
+    d_b = dev(B)
+    out = torch.full((p.m, B.shape[1]), float("nan"), dtype=out_dtype, device="cuda")
+    _lib.check(lib.onebit_matmul_packed(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(),
+                                        p.d_scale.data_ptr() if use_scale else None, d_b.data_ptr(), out.data_ptr(),
+                                        p.m, B.shape[1], p.k, _lib.OUT_F16 if out_dtype == torch.float16 else _lib.OUT_F32,
+                                        kernel, None))
+    _lib.check(lib.onebit_check_device_status())
+    return out.cpu().numpy()
+
+
+def check_exact_and_tolerance(lib, p, n, kernel, sigma=1.0):
+    # exact: integer tokens, no scale, fp32 out
+    B = helpers.make_tokens(p.rng, p.k, n, "int")
+    want32, _ = p.oracle(B, use_scale=False)
+    got = run_packed(lib, p, B, torch.float32, kernel, use_scale=False)
+    assert (got == want32).all(), f"max abs diff {np.abs(got - want32).max()}"
+    # tolerance: normal tokens, per-row scale, fp16 out
+    B = helpers.make_tokens(p.rng, p.k, n, "normal", sigma)
+    want32, want16 = p.oracle(B, use_scale=True)
+    got = run_packed(lib, p, B, torch.float16, kernel, use_scale=True)
+    ok, worst = helpers.row_tolerance_ok(got, want32)
+    assert ok, f"worst err / bound = {worst}"
+    assert np.isfinite(got).all()
+
+
+# ---- plain kernel on the reference orders: bit-exact in every case (same summation order) ------------
+
+@pytest.mark.parametrize("m,n,k,dialect", [(64, 8, 64, _lib.META_PYTHON), (192, 5, 96, _lib.META_PYTHON),
+                                           (96, 33, 160, _lib.META_CUTLASS), (32, 1, 32, _lib.META_CUTLASS)])
+def test_plain_kernel_bit_exact(lib, m, n, k, dialect):
+    p = Problem(11 + m, m, k, dialect)
+    B = helpers.make_tokens(p.rng, k, n)
+    want32, want16 = p.oracle(B, use_scale=True)
+    d_b = dev(B)
+    for dtype, want, code in ((torch.float32, want32, _lib.OUT_F32), (torch.float16, want16, _lib.OUT_F16)):
+        out = torch.zeros((m, n), dtype=dtype, device="cuda")
+        _lib.check(lib.onebit_sparse_matmul_ex(p.d_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), p.d_meta.data_ptr(),
+                                               p.d_scale.data_ptr(), m, n, k, code, dialect, None, 0, None))
+        assert (out.cpu().numpy() == want).all()
+
+
+# ---- decode kernel: config 2 shapes (7B-class linear layers), n in {1, 4, 8, 16} ------------------------
+
+@pytest.mark.parametrize("m,k", [(4096, 4096), (11008, 4096), (4096, 11008)])
+@pytest.mark.parametrize("n", [1, 4, 8, 16])
+def test_decode_kernel_config2(lib, m, k, n):
+    check_exact_and_tolerance(lib, Problem(m + k + n, m, k), n, _lib.KERNEL_DECODE)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 1, 128), (128, 3, 256), (256, 16, 1152), (384, 40, 640), (128, 9, 128 * 37)])
+def test_decode_kernel_ragged(lib, m, n, k):
+    check_exact_and_tolerance(lib, Problem(m * 3 + k + n, m, k), n, _lib.KERNEL_DECODE)
+
+
+# ---- tensor-memory kernel: config 0, reduced config 1 / 3 shapes, ragged n -------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (128, 128, 512), (512, 512, 512), (1024, 1024, 1024),
+                                   (256, 2048, 1024), (2048, 2048, 2048)])
+def test_prefill_kernel_squares(lib, m, n, k):
+    check_exact_and_tolerance(lib, Problem(m + n + k, m, k), n, _lib.KERNEL_PREFILL, sigma=0.5 if n == 2048 else 1.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 8, 128), (128, 24, 256), (256, 72, 384), (128, 200, 640), (384, 136, 128)])
+def test_prefill_kernel_ragged_n(lib, m, n, k):
+    check_exact_and_tolerance(lib, Problem(m + 5 * n + k, m, k), n, _lib.KERNEL_PREFILL)
+
+
+# ---- dispatcher and the stateless entry points ---------------------------------------------------------------
+
+@pytest.mark.parametrize("n", [1, 16, 17, 64])
+@pytest.mark.parametrize("dialect", [_lib.META_PYTHON, _lib.META_CUTLASS])
+def test_stateless_entry_point_dispatch(lib, n, dialect):
+    m, k = 256, 512
+    p = Problem(100 + n, m, k, dialect)
+    B = helpers.make_tokens(p.rng, k, n, "int")
+    want32, _ = p.oracle(B, use_scale=False)
+    d_b = dev(B)
+    out = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    ws = torch.zeros(lib.onebit_workspace_bytes(m, k), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.onebit_sparse_matmul_ex(p.d_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), p.d_meta.data_ptr(), None,
+                                           m, n, k, _lib.OUT_F32, dialect, ws.data_ptr(), ws.numel(), None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want32).all()
+    # library-owned scratch
+    out.zero_()
+    _lib.check(lib.onebit_sparse_matmul_ex(p.d_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), p.d_meta.data_ptr(), None,
+                                           m, n, k, _lib.OUT_F32, dialect, None, 0, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want32).all()
+
+
+def test_reference_entry_point(lib):
+    # the reference's own symbol: CUTLASS-ordered metadata, fp32 D, c ignored, default stream
+    m, n, k = 256, 64, 256
+    p = Problem(7, m, k, _lib.META_CUTLASS)
+    B = helpers.make_tokens(p.rng, k, n, "int")
+    want32, _ = p.oracle(B, use_scale=False)
+    d_b = dev(B)
+    out = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    getattr(lib, _lib.LEGACY_SYMBOL)(p.d_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), out.data_ptr(), p.d_meta.data_ptr(), m, n, k)
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want32).all()
+
+
+def test_reference_cli_degenerate_fill(lib):
+    # the reference CLI's default data: all sign bits 1, metadata 0x4444 everywhere
+    # (tests/kernel_test.cu:302-306,398-400): C[i, j] = sum_g B[4g, j] + B[4g + 1, j]
+    m, n, k = 128, 32, 256
+    a_bits = torch.full((k // 2, m // 8), 0xFF, dtype=torch.uint8, device="cuda")
+    e_meta = torch.full((m, k // 16), 0x4444, dtype=torch.int16, device="cuda")
+    B = np.random.default_rng(3).integers(-8, 9, size=(k, n)).astype(np.float16)
+    d_b = dev(B)
+    out = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    _lib.check(lib.onebit_sparse_matmul_ex(a_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), e_meta.data_ptr(), None,
+                                           m, n, k, _lib.OUT_F32, _lib.META_CUTLASS, None, 0, None))
+    _lib.check(lib.onebit_check_device_status())
+    want = B.astype(np.float32).reshape(k // 4, 4, n)[:, :2].sum(axis=(0, 1))
+    assert (out.cpu().numpy() == want[None, :]).all()
+
+
+def test_python_module_forward(lib):
+    import onebitsparsemul_b200 as ob
+    rng = np.random.default_rng(21)
+    m, k = 256, 384
+    dense, scale = helpers.make_weights(rng, m, k)
+    w = torch.from_numpy(dense * np.float16(0.5))
+    layer = ob.BinaryLinear_2_4(k, m).cuda()
+    with pytest.raises(NotImplementedError):
+        layer(torch.zeros((k, 8), dtype=torch.float16, device="cuda"))
+    layer.pack(w, scale=torch.from_numpy(scale))
+    canon, signs, _ = oracle.compress(dense)
+    for n in (4, 64):
+        B = helpers.make_tokens(rng, k, n, "int")
+        want32, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), 0, B, m, scale=scale)
+        got = layer(dev(B)).cpu().numpy()
+        assert np.allclose(got, want32, rtol=1e-6, atol=1e-6)
+        got2 = ob.cuda_binary_mul(layer.packed_binary_sparse, dev(B), layer.meta, scale=layer.scale).cpu().numpy()
+        assert (got2 == got).all()
