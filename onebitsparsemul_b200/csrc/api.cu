@@ -128,6 +128,11 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
 
 }  // namespace
 
+namespace ob {
+// lets the other translation units of the library report through onebit_last_error()
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace ob
+
 extern "C" {
 
 const char* onebit_last_error(void) { return g_err; }

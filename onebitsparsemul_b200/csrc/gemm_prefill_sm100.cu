@@ -19,24 +19,34 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include "formats.h"
 #include "kernels.h"
 
 namespace {
 
-constexpr int BM = 128;             // weight rows per CTA
+constexpr int BM = 128;             // weight rows per MMA (one weight tile)
 constexpr int BK = 128;             // dense k per stage = one weight tile
-constexpr int kNumThreads = 320;    // warp 0 producer, 1 MMA, 2-5 expander, 6-9 epilogue
 
-template <int BN> struct Cfg {
-  static constexpr int kABytes = BM * 128;                 // 128 rows x 64 fp16
+// MS  = weight tiles (128 rows each) stacked per CTA: the token tile in shared memory is reused by MS
+//       MMAs, which divides the L2 -> SM traffic per flop by MS (the weight stream is almost free)
+// BN  = tokens per CTA
+// NXG = expander groups of 4 warps; group g expands the (stage, tile) items with item % NXG == g, so
+//       that the proxy fence and barrier latency of one item overlaps the next item's work
+template <int MS, int BN, int NXG> struct Cfg {
+  static constexpr int kABytes = BM * 128;                 // 128 rows x 64 fp16, per weight tile
   static constexpr int kBBoxBytes = BK * 128;              // 128 k-rows x 64 tokens x 2 B
   static constexpr int kBBytes = (BN / 64) * kBBoxBytes;
-  static constexpr int kStageBytes = kABytes + kBBytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
-  static constexpr int kStages = (BN == 128) ? 4 : 2;
-  static constexpr int kTxBytes = kBBytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
-  static constexpr int kTmemCols = (BN == 128) ? 256 : 512;
+  static constexpr int kStageBytes = MS * (kABytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES) + kBBytes;
+  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;
+  static constexpr int kTxBytes = kBBytes + MS * (OB_TILE_META_BYTES + OB_TILE_BITS_BYTES);
+  static constexpr int kAccCols = MS * BN;
+  static constexpr int kTmemCols = (kAccCols + MS * 8 <= 128) ? 128 : (kAccCols + MS * 8 <= 256) ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kThreads = 32 * (2 + 4 * NXG + 4);   // producer, MMA, expanders, epilogue
+  static_assert(kAccCols + MS * 8 <= 512, "accumulators and metadata exceed tensor memory");
+  static_assert(kStages >= 2, "at least two stages");
 };
 
 struct PrefillArgs {
@@ -71,21 +81,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-// Bounded wait. `budget_ns` is this thread's remaining patience; once a wait has run out the
-// thread stops waiting for anything (budget 0), records `code` and lets the kernel drain.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, uint64_t& budget_ns, int* status, int code) {
+// Bounded wait. `budget` is this thread's remaining patience in SM clock cycles; once a wait has
+// run out the thread stops waiting for anything (budget 0), records `code` and lets the kernel
+// drain. The clock is read only every 64 polls: the poll itself is the hot path.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, long long& budget, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return;
-  if (budget_ns == 0) return;
-  const uint64_t start = globaltimer_ns();
+  if (budget == 0) return;
+  const long long start = clock64();
+  unsigned polls = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (globaltimer_ns() - start > budget_ns) {
-      budget_ns = 0;
+    if ((++polls & 63u) == 0 && clock64() - start > budget) {
+      budget = 0;
       atomicCAS(status, 0, code);
       return;
     }
@@ -152,19 +158,19 @@ __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
 
 // ---- the kernel -------------------------------------------------------------------------------
 
-template <int BN>
-__global__ void __launch_bounds__(kNumThreads, 1)
+template <int MS, int BN, int NXG>
+__global__ void __launch_bounds__(Cfg<MS, BN, NXG>::kThreads, 1)
 ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a) {
-  using C = Cfg<BN>;
+  using C = Cfg<MS, BN, NXG>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-  // stage s: [A 16 KiB][B BN/64 x 16 KiB][meta 2 KiB][bits 1 KiB]
-  auto stage_a = [&](int s) { return smem_base + s * C::kStageBytes; };
-  auto stage_b = [&](int s) { return stage_a(s) + C::kABytes; };
-  auto stage_e = [&](int s) { return stage_b(s) + C::kBBytes; };
-  auto stage_bits = [&](int s) { return stage_e(s) + OB_TILE_META_BYTES; };
+  // stage s: [A x MS, 16 KiB each][B BN/64 x 16 KiB][meta x MS, 2 KiB each][bits x MS, 1 KiB each]
+  auto stage_a = [&](int s, int t) { return smem_base + s * C::kStageBytes + t * C::kABytes; };
+  auto stage_b = [&](int s) { return smem_base + s * C::kStageBytes + MS * C::kABytes; };
+  auto stage_e = [&](int s, int t) { return stage_b(s) + C::kBBytes + t * OB_TILE_META_BYTES; };
+  auto stage_bits = [&](int s, int t) { return stage_b(s) + C::kBBytes + MS * OB_TILE_META_BYTES + t * OB_TILE_BITS_BYTES; };
   const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
   auto bar_full = [&](int s) { return bar_base + 8 * s; };                       // TMA landed
   auto bar_afull = [&](int s) { return bar_base + 8 * (C::kStages + s); };       // +-1 values written
@@ -174,13 +180,13 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t mb = blockIdx.x;
+  const int64_t mb = blockIdx.x;                  // block of MS weight tiles
   const int64_t n0 = (int64_t)blockIdx.y * BN;
   const int kt = (int)(a.k / BK);
-  uint64_t budget = 1000000000ull;   // ns
+  long long budget = 2000000000ll;                // cycles, about a second
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_afull(s), 128); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_afull(s), 128 * MS); mbar_init(bar_empty(s), 1); }
     mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
@@ -190,14 +196,12 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
-  const uint32_t tmem_acc = tmem_base;                 // columns [0, BN)
-  const uint32_t tmem_e = tmem_base + BN;              // two 4-column metadata slots
+  const uint32_t tmem_acc = tmem_base;                 // MS accumulators of BN columns
+  const uint32_t tmem_e = tmem_base + C::kAccCols;     // per weight tile two 4-column metadata slots
 
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      const uint8_t* meta_src = a.meta_tile + (mb * kt) * (int64_t)OB_TILE_META_BYTES;
-      const uint8_t* bits_src = a.bits_tile + (mb * kt) * (int64_t)OB_TILE_BITS_BYTES;
       for (int it = 0; it < kt; ++it) {
         const int s = it % C::kStages;
         mbar_wait(bar_empty(s), ((it / C::kStages) & 1) ^ 1, budget, a.status, 1);
@@ -205,8 +209,12 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
 #pragma unroll
         for (int j = 0; j < BN / 64; ++j)
           tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * BK, bar_full(s));
-        bulk_load(stage_e(s), meta_src + (int64_t)it * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
-        bulk_load(stage_bits(s), bits_src + (int64_t)it * OB_TILE_BITS_BYTES, OB_TILE_BITS_BYTES, bar_full(s));
+#pragma unroll
+        for (int t = 0; t < MS; ++t) {
+          const int64_t tile = (mb * MS + t) * kt + it;
+          bulk_load(stage_e(s, t), a.meta_tile + tile * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
+          bulk_load(stage_bits(s, t), a.bits_tile + tile * OB_TILE_BITS_BYTES, OB_TILE_BITS_BYTES, bar_full(s));
+        }
       }
     }
   } else if (warp == 1) {
@@ -220,29 +228,34 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
         mbar_wait(bar_full(s), ph, budget, a.status, 2);
         mbar_wait(bar_afull(s), ph, budget, a.status, 3);
         tcgen05_fence_after();
-        const uint32_t e_col = tmem_e + 4 * (it & 1);
-        tcgen05_cp_128x128b(e_col, make_desc(stage_e(s), 128, 128, kLayoutNone));
-        const uint64_t adesc = make_desc(stage_a(s), 16, 1024, kLayoutSw128);
         const uint64_t bdesc = make_desc(stage_b(s), C::kBBoxBytes, 1024, kLayoutSw128);
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-          // k-block kb: 32 bytes further along the swizzled A rows, 32 k-rows (4 KiB) further in B,
-          // metadata column kb = even column address + id2
-          tcgen05_mma_sp_f16(tmem_acc, adesc + (uint64_t)(2 * kb), bdesc + (uint64_t)(256 * kb),
-                             e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
+        for (int t = 0; t < MS; ++t) {
+          const uint32_t e_col = tmem_e + 8 * t + 4 * (it & 1);
+          tcgen05_cp_128x128b(e_col, make_desc(stage_e(s, t), 128, 128, kLayoutNone));
+          const uint64_t adesc = make_desc(stage_a(s, t), 16, 1024, kLayoutSw128);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            // k-block kb: 32 bytes further along the swizzled A rows, 32 k-rows (4 KiB) further in B,
+            // metadata column kb = even column address + id2
+            tcgen05_mma_sp_f16(tmem_acc + t * BN, adesc + (uint64_t)(2 * kb), bdesc + (uint64_t)(256 * kb),
+                               e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
+          }
         }
         tcgen05_commit(bar_empty(s));
       }
       tcgen05_commit(bar_acc);
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + 4 * NXG) {
     // ---------------- expander: thread = weight row ----------------
-    const int r = (warp - 2) * 32 + lane;
-    for (int it = 0; it < kt; ++it) {
+    const int xg = (warp - 2) >> 2;                       // expander group
+    const int r = ((warp - 2) & 3) * 32 + lane;
+    for (int item = xg; item < kt * MS; item += NXG) {
+      const int it = item / MS, t = item % MS;
       const int s = it % C::kStages;
       mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 4);
-      const uint2 w = *reinterpret_cast<const uint2*>(smem_gen + (stage_bits(s) - smem_base) + r * 8);
-      uint8_t* arow = smem_gen + (stage_a(s) - smem_base) + r * 128;
+      const uint2 w = *reinterpret_cast<const uint2*>(smem_gen + (stage_bits(s, t) - smem_base) + r * 8);
+      uint8_t* arow = smem_gen + (stage_a(s, t) - smem_base) + r * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
         const uint32_t word = (c < 4) ? w.x : w.y;
@@ -261,37 +274,40 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
     const int q = warp & 3;
     mbar_wait(bar_acc, 0, budget, a.status, 5);
     tcgen05_fence_after();
-    const int64_t row = mb * BM + q * 32 + lane;
-    const float sc = a.scale ? __half2float(a.scale[row]) : 1.f;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      uint32_t v[32];
-      tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
-      const int64_t col = n0 + c0;
-      if (col >= a.n) continue;
-      if (a.out_type == OB_OUT_F16) {
-        __half* dst = static_cast<__half*>(a.d) + row * a.n + col;
+    for (int t = 0; t < MS; ++t) {
+      const int64_t row = (mb * MS + t) * BM + q * 32 + lane;
+      const float sc = a.scale ? __half2float(a.scale[row]) : 1.f;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * BN + c0), v);
+        const int64_t col = n0 + c0;
+        if (col >= a.n) continue;
+        if (a.out_type == OB_OUT_F16) {
+          __half* dst = static_cast<__half*>(a.d) + row * a.n + col;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (col + 8 * j < a.n) {
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+          for (int j = 0; j < 4; ++j) {
+            if (col + 8 * j < a.n) {
+              uint4 o;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
-              ow[h] = *reinterpret_cast<const uint32_t*>(&p);
+              for (int h = 0; h < 4; ++h) {
+                const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
+                ow[h] = *reinterpret_cast<const uint32_t*>(&p);
+              }
+              *reinterpret_cast<uint4*>(dst + 8 * j) = o;
             }
-            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
           }
-        }
-      } else {
-        float* dst = static_cast<float*>(a.d) + row * a.n + col;
+        } else {
+          float* dst = static_cast<float*>(a.d) + row * a.n + col;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          if (col + 4 * j < a.n) {
-            float4 o = make_float4(__uint_as_float(v[4 * j]) * sc, __uint_as_float(v[4 * j + 1]) * sc,
-                                   __uint_as_float(v[4 * j + 2]) * sc, __uint_as_float(v[4 * j + 3]) * sc);
-            *reinterpret_cast<float4*>(dst + 4 * j) = o;
+          for (int j = 0; j < 8; ++j) {
+            if (col + 4 * j < a.n) {
+              float4 o = make_float4(__uint_as_float(v[4 * j]) * sc, __uint_as_float(v[4 * j + 1]) * sc,
+                                     __uint_as_float(v[4 * j + 2]) * sc, __uint_as_float(v[4 * j + 3]) * sc);
+              *reinterpret_cast<float4*>(dst + 4 * j) = o;
+            }
           }
         }
       }
@@ -324,19 +340,19 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-template <int BN>
+template <int MS, int BN, int NXG>
 cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t stream) {
-  using C = Cfg<BN>;
+  using C = Cfg<MS, BN, NXG>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill_kernel<MS, BN, NXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  dim3 grid((unsigned)(a.m / BM), (unsigned)((a.n + BN - 1) / BN));
-  ob_gemm_prefill_kernel<BN><<<grid, kNumThreads, C::kSmemBytes, stream>>>(tmap, a);
+  dim3 grid((unsigned)(a.m / (BM * MS)), (unsigned)((a.n + BN - 1) / BN));
+  ob_gemm_prefill_kernel<MS, BN, NXG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, a);
   return cudaGetLastError();
 }
 
@@ -365,7 +381,21 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
     return cudaErrorInvalidValue;
   PrefillArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                 static_cast<const __half*>(scale), d, m, n, k, out_type, status};
-  return launch<128>(tmap, a, stream);
+  // tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <MS><BN/64><NXG>, e.g. 222 = 2 tiles, 128 tokens, 2 groups
+  static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
+  const bool two = (m % 256 == 0);
+  switch (forced) {
+    case 121: return launch<1, 128, 1>(tmap, a, stream);
+    case 122: return launch<1, 128, 2>(tmap, a, stream);
+    case 141: return launch<1, 256, 1>(tmap, a, stream);
+    case 142: return launch<1, 256, 2>(tmap, a, stream);
+    case 221: if (two) return launch<2, 128, 1>(tmap, a, stream); break;
+    case 222: if (two) return launch<2, 128, 2>(tmap, a, stream); break;
+    case 224: if (two) return launch<2, 128, 4>(tmap, a, stream); break;
+    case 212: if (two) return launch<2, 64, 2>(tmap, a, stream); break;
+    default: break;
+  }
+  return launch<1, 128, 1>(tmap, a, stream);
 }
 
 }  // namespace ob
