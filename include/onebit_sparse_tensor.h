@@ -109,6 +109,21 @@ int onebit_mask24(const void *dense_f16, int64_t count, void *masked_f16, void *
 int onebit_unpack_to_dense(const void *bits_tile, const void *meta_tile, const void *scale, int64_t m, int64_t k,
                            void *dense_f16, void *stream);
 
+/* The stateless GEMM for callers that cannot allocate device memory -- a server whose own pool owns
+ * the whole GPU, a decode loop that cannot take cudaMalloc's device-wide synchronisation, a host that
+ * forbids allocation after start-up. No counterpart in the reference (its entry point allocates a
+ * CUTLASS workspace object per call, csrc/kernel_lib.cu:73-76). Same operands as
+ * onebit_sparse_matmul_ex, but the tile-ordered copy of the weights goes into a fixed array inside
+ * the library image (held by every GPU that loads the library, until exit) instead of a workspace:
+ *   - m * k <= ONEBIT_STATIC_MAX_WEIGHTS, m % 128 == 0, k % 128 == 0, else an error and no launch;
+ *   - always the split-K cluster kernel (meant for few tokens; any n works);
+ *   - the first call per device fetches the array's device address: make it outside stream capture;
+ *   - calls share the array: two calls that overlap on the GPU race -- serialise them;
+ *   - never calls cudaMalloc / cudaFree or an allocating library routine. */
+#define ONEBIT_STATIC_MAX_WEIGHTS (4096LL * 11008LL)
+int onebit_sparse_matmul_static(const void *a_bits, const void *b, void *d, const void *e_meta, const void *scale,
+                                int64_t m, int64_t n, int64_t k, int out_type, int meta_dialect, void *stream);
+
 /* Synchronises the current device, then reads and clears its status word: ONEBIT_ERR_DEVICE_WAIT if
  * a bounded wait inside the tensor-memory kernel gave up since the last call (the kernel then still
  * terminated, with an unusable result), ONEBIT_OK otherwise. The reference has no counterpart; its

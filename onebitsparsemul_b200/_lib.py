@@ -24,6 +24,7 @@ SIGNATURES = {
     "onebit_packed_meta_bytes": (_sz, [_i64, _i64]),
     "onebit_workspace_bytes": (_sz, [_i64, _i64]),
     "onebit_sparse_matmul_ex": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _sz, _vp]),
+    "onebit_sparse_matmul_static": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "onebit_relayout": (_int, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp]),
     "onebit_matmul_packed": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "onebit_pack_from_dense": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
