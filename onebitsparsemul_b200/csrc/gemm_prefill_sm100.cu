@@ -7,10 +7,12 @@
 //                   map, and the tile-ordered sign bits (1 KiB) and metadata (2 KiB) of the
 //                   128x128 weight tile as plain bulk copies; one mbarrier transaction per stage
 //   expander warps  thread = weight row: 64 sign bits -> 64 exact fp16 +-1 values (one shift and
-//                   one logic op per pair), written K-major with the 128-byte swizzle
+//                   one logic op per pair), stored with tcgen05.st into a ring of tensor-memory
+//                   slots (or, in the shared-memory form, K-major with the 128-byte swizzle)
 //   MMA thread      tcgen05.cp moves the metadata block into 4 tensor-memory columns, then
-//                   4 x tcgen05.mma.sp.kind::f16 (M=128, N=BN, K=32 dense) per stage, fp32
-//                   accumulators in tensor memory; tcgen05.commit frees the stage
+//                   4 x tcgen05.mma.sp.kind::f16 (M=128, N=BN, K=32 dense) per weight tile and stage
+//                   with the +-1 operand read from tensor memory, fp32 accumulators in tensor
+//                   memory; tcgen05.commit frees the stage and the operand slot
 //   epilogue warps  tcgen05.ld -> per-row scale -> fp16 / fp32 -> 16-byte global stores
 //
 // Every wait on an mbarrier is bounded: after ~1 s a thread records a code in the status word and
@@ -34,19 +36,30 @@ constexpr int BK = 128;             // dense k per stage = one weight tile
 // BN  = tokens per CTA
 // NXG = expander groups of 4 warps; group g expands the (stage, tile) items with item % NXG == g, so
 //       that the proxy fence and barrier latency of one item overlaps the next item's work
-template <int MS, int BN, int NXG> struct Cfg {
-  static constexpr int kABytes = BM * 128;                 // 128 rows x 64 fp16, per weight tile
+// AT  = where the expanded +-1 operand lives: false = shared memory (K-major, 128-byte swizzle),
+//       true = tensor memory (tcgen05.st by the expander, A-from-TMEM form of the MMA). The TMEM
+//       form takes the A operand off the shared-memory port entirely (no expander writes, no MMA
+//       reads), which is the port this kernel saturates first.
+template <int MS, int BN, int NXG, bool AT> struct Cfg {
+  static constexpr int kABytes = AT ? 0 : BM * 128;        // 128 rows x 64 fp16, per weight tile
   static constexpr int kBBoxBytes = BK * 128;              // 128 k-rows x 64 tokens x 2 B
   static constexpr int kBBytes = (BN / 64) * kBBoxBytes;
   static constexpr int kStageBytes = MS * (kABytes + OB_TILE_META_BYTES + OB_TILE_BITS_BYTES) + kBBytes;
-  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;
+  static constexpr int kStagesFit = (227 * 1024 - 2048) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
   static constexpr int kTxBytes = kBBytes + MS * (OB_TILE_META_BYTES + OB_TILE_BITS_BYTES);
   static constexpr int kAccCols = MS * BN;
-  static constexpr int kTmemCols = (kAccCols + MS * 8 <= 128) ? 128 : (kAccCols + MS * 8 <= 256) ? 256 : 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int kECols = MS * 8;                    // per weight tile two 4-column metadata slots
+  static constexpr int kASlotCols = MS * 32;               // TMEM form: 64 fp16 per row and weight tile
+  static constexpr int kASlotsFit = AT ? (512 - kAccCols - kECols) / kASlotCols : 0;
+  // ring of +-1 operand slots: the stages themselves (smem form) or up to 4 TMEM slots
+  static constexpr int kASlots = AT ? (kASlotsFit > 4 ? 4 : kASlotsFit) : kStages;
+  static constexpr int kUsedCols = kAccCols + kECols + (AT ? kASlots * kASlotCols : 0);
+  static constexpr int kTmemCols = kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 512 /*barriers*/;
   static constexpr int kThreads = 32 * (2 + 4 * NXG + 4);   // producer, MMA, expanders, epilogue
-  static_assert(kAccCols + MS * 8 <= 512, "accumulators and metadata exceed tensor memory");
-  static_assert(kStages >= 2, "at least two stages");
+  static_assert(kUsedCols <= 512, "accumulators, metadata and operand slots exceed tensor memory");
+  static_assert(kStages >= 2 && kASlots >= 2, "at least two stages and two operand slots");
 };
 
 struct PrefillArgs {
@@ -132,6 +145,27 @@ __device__ __forceinline__ void tcgen05_mma_sp_f16(uint32_t d_tmem, uint64_t ade
       "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same MMA with the compressed +-1 operand read from tensor memory (lane = row, two fp16 per column)
+__device__ __forceinline__ void tcgen05_mma_sp_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t e_tmem,
+                                                      uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [%1], %2, [%3], %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tcgen05_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -158,24 +192,25 @@ __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
 
 // ---- the kernel -------------------------------------------------------------------------------
 
-template <int MS, int BN, int NXG>
-__global__ void __launch_bounds__(Cfg<MS, BN, NXG>::kThreads, 1)
+template <int MS, int BN, int NXG, bool AT>
+__global__ void __launch_bounds__(Cfg<MS, BN, NXG, AT>::kThreads, 1)
 ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a) {
-  using C = Cfg<MS, BN, NXG>;
+  using C = Cfg<MS, BN, NXG, AT>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
-  // stage s: [A x MS, 16 KiB each][B BN/64 x 16 KiB][meta x MS, 2 KiB each][bits x MS, 1 KiB each]
+  // stage s: [A x MS, 16 KiB each (smem form only)][B BN/64 x 16 KiB][meta x MS, 2 KiB each][bits x MS, 1 KiB each]
   auto stage_a = [&](int s, int t) { return smem_base + s * C::kStageBytes + t * C::kABytes; };
   auto stage_b = [&](int s) { return smem_base + s * C::kStageBytes + MS * C::kABytes; };
   auto stage_e = [&](int s, int t) { return stage_b(s) + C::kBBytes + t * OB_TILE_META_BYTES; };
   auto stage_bits = [&](int s, int t) { return stage_b(s) + C::kBBytes + MS * OB_TILE_META_BYTES + t * OB_TILE_BITS_BYTES; };
   const uint32_t bar_base = smem_base + C::kStages * C::kStageBytes;
-  auto bar_full = [&](int s) { return bar_base + 8 * s; };                       // TMA landed
-  auto bar_afull = [&](int s) { return bar_base + 8 * (C::kStages + s); };       // +-1 values written
-  auto bar_empty = [&](int s) { return bar_base + 8 * (2 * C::kStages + s); };   // MMAs of the stage done
-  const uint32_t bar_acc = bar_base + 8 * (3 * C::kStages);
+  auto bar_full = [&](int s) { return bar_base + 8 * s; };                        // TMA landed
+  auto bar_empty = [&](int s) { return bar_base + 8 * (C::kStages + s); };        // MMAs of the stage done
+  auto bar_afull = [&](int x) { return bar_base + 8 * (2 * C::kStages + x); };    // +-1 values written to slot x
+  auto bar_aempty = [&](int x) { return bar_base + 8 * (2 * C::kStages + C::kASlots + x); };  // MMAs reading slot x done
+  const uint32_t bar_acc = bar_base + 8 * (2 * C::kStages + 2 * C::kASlots);
   const uint32_t tmem_slot = bar_acc + 8;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
@@ -186,7 +221,8 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
   long long budget = 2000000000ll;                // cycles, about a second
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_afull(s), 128 * MS); mbar_init(bar_empty(s), 1); }
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+    for (int x = 0; x < C::kASlots; ++x) { mbar_init(bar_afull(x), 128 * MS); mbar_init(bar_aempty(x), 1); }
     mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
@@ -196,8 +232,9 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_gen;
-  const uint32_t tmem_acc = tmem_base;                 // MS accumulators of BN columns
-  const uint32_t tmem_e = tmem_base + C::kAccCols;     // per weight tile two 4-column metadata slots
+  const uint32_t tmem_acc = tmem_base;                           // MS accumulators of BN columns
+  const uint32_t tmem_e = tmem_base + C::kAccCols;               // metadata slots
+  const uint32_t tmem_a = tmem_base + C::kAccCols + C::kECols;   // +-1 operand slots (TMEM form)
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -223,10 +260,9 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
       const uint32_t idesc = (1u << 2) /*sparse*/ | (1u << 4) /*fp32 accumulate*/ | (1u << 16) /*B is n-major*/ |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       for (int it = 0; it < kt; ++it) {
-        const int s = it % C::kStages;
-        const uint32_t ph = (it / C::kStages) & 1;
-        mbar_wait(bar_full(s), ph, budget, a.status, 2);
-        mbar_wait(bar_afull(s), ph, budget, a.status, 3);
+        const int s = it % C::kStages, x = it % C::kASlots;
+        mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 2);
+        mbar_wait(bar_afull(x), (it / C::kASlots) & 1, budget, a.status, 3);
         tcgen05_fence_after();
         const uint64_t bdesc = make_desc(stage_b(s), C::kBBoxBytes, 1024, kLayoutSw128);
 #pragma unroll
@@ -236,38 +272,58 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
           const uint64_t adesc = make_desc(stage_a(s, t), 16, 1024, kLayoutSw128);
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
-            // k-block kb: 32 bytes further along the swizzled A rows, 32 k-rows (4 KiB) further in B,
-            // metadata column kb = even column address + id2
-            tcgen05_mma_sp_f16(tmem_acc + t * BN, adesc + (uint64_t)(2 * kb), bdesc + (uint64_t)(256 * kb),
-                               e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
+            // k-block kb: 32 k-rows (4 KiB) further in B; metadata column kb = even column address + id2;
+            // the +-1 operand 32 bytes further along its swizzled smem rows, or 8 TMEM columns further
+            if constexpr (AT)
+              tcgen05_mma_sp_f16_ts(tmem_acc + t * BN, tmem_a + x * C::kASlotCols + t * 32 + 8 * kb, bdesc + (uint64_t)(256 * kb),
+                                    e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
+            else
+              tcgen05_mma_sp_f16(tmem_acc + t * BN, adesc + (uint64_t)(2 * kb), bdesc + (uint64_t)(256 * kb),
+                                 e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (it | kb) != 0);
           }
         }
         tcgen05_commit(bar_empty(s));
+        if constexpr (AT) tcgen05_commit(bar_aempty(x));
       }
       tcgen05_commit(bar_acc);
     }
   } else if (warp < 2 + 4 * NXG) {
-    // ---------------- expander: thread = weight row ----------------
+    // ---------------- expander: thread = weight row; the warp's TMEM quadrant is warp % 4 ----------------
     const int xg = (warp - 2) >> 2;                       // expander group
-    const int r = ((warp - 2) & 3) * 32 + lane;
-    for (int item = xg; item < kt * MS; item += NXG) {
-      const int it = item / MS, t = item % MS;
-      const int s = it % C::kStages;
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    for (int it = 0; it < kt; ++it) {
+      // every group passes every phase of the barriers it ever waits on (parity tracking)
+      const int s = it % C::kStages, x = it % C::kASlots;
       mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 4);
-      const uint2 w = *reinterpret_cast<const uint2*>(smem_gen + (stage_bits(s, t) - smem_base) + r * 8);
-      uint8_t* arow = smem_gen + (stage_a(s, t) - smem_base) + r * 128;
+      if constexpr (AT) mbar_wait(bar_aempty(x), ((it / C::kASlots) & 1) ^ 1, budget, a.status, 6);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint32_t word = (c < 4) ? w.x : w.y;
-        uint4 v;
-        v.x = expand_pair(word, 4 * (c & 3) + 0);
-        v.y = expand_pair(word, 4 * (c & 3) + 1);
-        v.z = expand_pair(word, 4 * (c & 3) + 2);
-        v.w = expand_pair(word, 4 * (c & 3) + 3);
-        *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;
+      for (int t = 0; t < MS; ++t) {
+        if ((it * MS + t) % NXG != xg) continue;
+        const uint2 w = *reinterpret_cast<const uint2*>(smem_gen + (stage_bits(s, t) - smem_base) + r * 8);
+        if constexpr (AT) {
+          uint32_t v[32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { v[j] = expand_pair(w.x, j); v[16 + j] = expand_pair(w.y, j); }
+          tcgen05_fence_after();
+          tcgen05_st_32x32b_x32(tmem_a + ((uint32_t)(q * 32) << 16) + (uint32_t)(x * C::kASlotCols + t * 32), v);
+          tcgen05_fence_before();
+        } else {
+          uint8_t* arow = smem_gen + (stage_a(s, t) - smem_base) + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint32_t word = (c < 4) ? w.x : w.y;
+            uint4 v;
+            v.x = expand_pair(word, 4 * (c & 3) + 0);
+            v.y = expand_pair(word, 4 * (c & 3) + 1);
+            v.z = expand_pair(word, 4 * (c & 3) + 2);
+            v.w = expand_pair(word, 4 * (c & 3) + 3);
+            *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        mbar_arrive(bar_afull(x));
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(bar_afull(s));
     }
   } else {
     // ---------------- epilogue: warp quadrant = warp % 4, thread = output row ----------------
@@ -340,19 +396,19 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-template <int MS, int BN, int NXG>
+template <int MS, int BN, int NXG, bool AT>
 cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t stream) {
-  using C = Cfg<MS, BN, NXG>;
+  using C = Cfg<MS, BN, NXG, AT>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill_kernel<MS, BN, NXG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill_kernel<MS, BN, NXG, AT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
   dim3 grid((unsigned)(a.m / (BM * MS)), (unsigned)((a.n + BN - 1) / BN));
-  ob_gemm_prefill_kernel<MS, BN, NXG><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, a);
+  ob_gemm_prefill_kernel<MS, BN, NXG, AT><<<grid, C::kThreads, C::kSmemBytes, stream>>>(tmap, a);
   return cudaGetLastError();
 }
 
@@ -381,21 +437,28 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
     return cudaErrorInvalidValue;
   PrefillArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                 static_cast<const __half*>(scale), d, m, n, k, out_type, status};
-  // tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <MS><BN/64><NXG>, e.g. 222 = 2 tiles, 128 tokens, 2 groups
+  // tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <AT><MS><BN/64><NXG>
   static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
   const bool two = (m % 256 == 0);
   switch (forced) {
-    case 121: return launch<1, 128, 1>(tmap, a, stream);
-    case 122: return launch<1, 128, 2>(tmap, a, stream);
-    case 141: return launch<1, 256, 1>(tmap, a, stream);
-    case 142: return launch<1, 256, 2>(tmap, a, stream);
-    case 221: if (two) return launch<2, 128, 1>(tmap, a, stream); break;
-    case 222: if (two) return launch<2, 128, 2>(tmap, a, stream); break;
-    case 224: if (two) return launch<2, 128, 4>(tmap, a, stream); break;
-    case 212: if (two) return launch<2, 64, 2>(tmap, a, stream); break;
+    case 121: return launch<1, 128, 1, false>(tmap, a, stream);
+    case 141: return launch<1, 256, 1, false>(tmap, a, stream);
+    case 221: if (two) return launch<2, 128, 1, false>(tmap, a, stream); break;
+    case 222: if (two) return launch<2, 128, 2, false>(tmap, a, stream); break;
+    case 1121: return launch<1, 128, 1, true>(tmap, a, stream);
+    case 1141: return launch<1, 256, 1, true>(tmap, a, stream);
+    case 1142: return launch<1, 256, 2, true>(tmap, a, stream);
+    case 1221: if (two) return launch<2, 128, 1, true>(tmap, a, stream); break;
+    case 1222: if (two) return launch<2, 128, 2, true>(tmap, a, stream); break;
     default: break;
   }
-  return launch<1, 128, 1>(tmap, a, stream);
+  // Shape heuristic. All default variants keep the +-1 operand in tensor memory. A 256-token tile
+  // halves the weight-side work per token and is the fastest once it fills the 148 SMs; otherwise
+  // two stacked weight tiles share a 128-token tile, or the smallest tile spreads a small problem.
+  const int64_t row_tiles = m / BM;
+  if (n > 128 && row_tiles * ((n + 255) / 256) >= 148) return launch<1, 256, 1, true>(tmap, a, stream);
+  if (two && (row_tiles / 2) * ((n + 127) / 128) >= 148) return launch<2, 128, 1, true>(tmap, a, stream);
+  return launch<1, 128, 1, true>(tmap, a, stream);
 }
 
 }  // namespace ob
