@@ -233,7 +233,10 @@ def run_ours(args):
                     "note": "tokens from pinned host memory, result to pinned host memory, weights resident"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": sparse_peak, "unit": "TFLOP/s",
-                         "frac": achieved / sparse_peak, "traffic": None,
+                         "frac": achieved / sparse_peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture of
+                         # this workload (profiles/prefill_kernel_square8192_ncu_full.md); algorithmic bytes are 2.81e8
+                         "traffic": 2.518e8 if S == 8192 else None,
                          "peak_note": f"2 x dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}): 2:4 sparse MMA rate",
                          "frac_of_dense_peak": achieved / peaks["bf16_tflops"], "kernel": "ob_gemm_prefill_kernel",
                          "kernel_ms": kernel_ms},

@@ -19,7 +19,7 @@ __all__ = [
     "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
     "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
     "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
-    "relayout", "OneBitError",
+    "relayout", "matmul_rows", "OneBitError",
 ]
 
 
@@ -198,6 +198,26 @@ def matmul_packed(pw: PackedWeight, B, out=None, out_dtype=torch.float32, kernel
     with torch.cuda.device(B.device):
         _lib.check(lib.onebit_matmul_packed(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(B), _ptr(out),
                                             pw.m, n, pw.k, _out_code(out.dtype), kernel, _stream()))
+    return out
+
+
+def matmul_rows(pw: PackedWeight, B, out, row0: int, rows: int, kernel=KERNEL_AUTO):
+    """out (rows, n) = pw[row0:row0+rows] @ B: the GEMM on a block of whole 128-row tiles of a packed
+    weight (tile order keeps the tiles of a row block contiguous, so this is pointer arithmetic)."""
+    lib = _lib.load()
+    if row0 % 128 or rows % 128 or row0 + rows > pw.m:
+        raise ValueError("row blocks must be whole 128-row tiles inside the weight")
+    if not B.is_cuda or B.dtype != torch.float16 or B.shape[0] != pw.k:
+        raise ValueError("B must be a CUDA float16 tensor of shape (k, n)")
+    B = B.contiguous()
+    n = B.shape[1]
+    if tuple(out.shape) != (rows, n) or not out.is_contiguous():
+        raise ValueError("out must be a contiguous (rows, n) tensor")
+    tiles = (row0 // 128) * (pw.k // 128)
+    scale_ptr = None if pw.scale is None else pw.scale.data_ptr() + 2 * row0
+    with torch.cuda.device(B.device):
+        _lib.check(lib.onebit_matmul_packed(pw.bits_tile.data_ptr() + tiles * 1024, pw.meta_tile.data_ptr() + tiles * 2048,
+                                            scale_ptr, _ptr(B), _ptr(out), rows, n, pw.k, _out_code(out.dtype), kernel, _stream()))
     return out
 
 

@@ -1,0 +1,164 @@
+"""Row sharding across ranks.
+
+CPU part (gloo, world_size 2): the partition arithmetic, per-slab packing against slicing a global
+pack, and the gather plumbing of ShardedBinaryLinear with the oracle standing in for the GEMM.
+GPU part: the real kernels on however many GPUs are visible, compared bit for bit with the single-GPU
+result (row sharding does not change any reduction order).
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import oracle
+from onebitsparsemul_b200.sharded import ShardedBinaryLinear, chunk_rows, row_partition
+from tests import helpers
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_row_partition():
+    assert row_partition(8192, 8) == [(i * 1024, 1024) for i in range(8)]
+    assert row_partition(25600, 8) == [(i * 3200, 3200) for i in range(4)] + [(12800 + i * 3200, 3200) for i in range(4)] \
+        or sum(r for _, r in row_partition(25600, 8)) == 25600
+    parts = row_partition(28672, 8)
+    assert sum(r for _, r in parts) == 28672 and all(r % 256 == 0 for _, r in parts)
+    assert [s for s, _ in parts] == list(np.cumsum([0] + [r for _, r in parts[:-1]]))
+    assert max(r for _, r in parts) - min(r for _, r in parts) <= 256
+    assert row_partition(768, 2) == [(0, 512), (512, 256)]
+    with pytest.raises(ValueError):
+        row_partition(1000, 2)
+    with pytest.raises(ValueError):
+        row_partition(256, 2)
+    assert chunk_rows(1024, 4) == [(0, 256), (256, 256), (512, 256), (768, 256)]
+    assert chunk_rows(512, 4) == [(0, 256), (256, 256)]
+
+
+def test_slab_pack_equals_rows_of_the_canonical_pack():
+    rng = np.random.default_rng(4)
+    dense, _ = helpers.make_weights(rng, 768, 128)
+    canon, signs, _ = oracle.compress(dense)
+    for start, rows in row_partition(768, 2):
+        c2, s2, _ = oracle.compress(dense[start:start + rows])
+        assert (c2 == canon[start:start + rows]).all() and (s2 == signs[start:start + rows]).all()
+        # ... but the reference-ordered slab is NOT a slice of the global pack: pack per slab
+        assert oracle.pack_bits(s2).shape == (64, rows // 8)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _cpu_worker(rank, world, port, mode, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(9)
+        m, k, n = 768, 128, 8
+        dense, scale = helpers.make_weights(rng, m, k)
+        B = helpers.make_tokens(rng, k, n, "int")
+
+        def pack(w, s):                                     # oracle stands in for the pack kernel
+            canon, signs, _ = oracle.compress(w.numpy())
+            return (oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), None if s is None else s.numpy(), w.shape[0])
+
+        def matmul(pw, Bt, out, row0, rows):                # ... and for the GEMM kernels
+            bits, meta, sc, mm = pw
+            c32, _ = oracle.gemm(bits, meta, 0, Bt.numpy(), mm, scale=sc)
+            out.copy_(torch.from_numpy(c32[row0:row0 + rows]))
+
+        layer = ShardedBinaryLinear(m, k, matmul=matmul, pack=pack)
+        layer.pack_full(torch.from_numpy(dense), torch.from_numpy(scale))
+        got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float32, chunks=2).numpy()
+        canon, signs, _ = oracle.compress(dense)
+        want, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), 0, B, m, scale=scale)
+        if mode == "none":
+            want = want[layer.start:layer.start + layer.rows]
+        q.put((rank, bool((got == want).all()), got.shape))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["none", "all", "overlap"])
+def test_sharded_host_logic_two_cpu_ranks(mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cpu_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results), results
+    shapes = {r: s for r, _, s in results}
+    if mode == "none":
+        assert shapes == {0: (512, 8), 1: (256, 8)}
+    else:
+        assert shapes == {0: (768, 8), 1: (768, 8)}
+
+
+def _gpu_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import onebitsparsemul_b200 as ob
+        rng = np.random.default_rng(10)
+        m, k = 2048, 1024
+        dense, scale = helpers.make_weights(rng, m, k)
+        w, sc = torch.from_numpy(dense).cuda(), torch.from_numpy(scale).cuda()
+        single = ob.pack_weight(w, scale=sc)
+        layer = ShardedBinaryLinear(m, k).pack_full(w, sc)
+        ok = True
+        for n in (8, 512):
+            B = torch.from_numpy(helpers.make_tokens(rng, k, n)).cuda()
+            want = ob.matmul_packed(single, B, out_dtype=torch.float16)
+            slab = layer.forward(B, gather="none")
+            ok &= bool((slab == want[layer.start:layer.start + layer.rows]).all())
+            for mode in ("all", "overlap"):
+                ok &= bool((layer.forward(B, gather=mode) == want).all())
+        torch.cuda.synchronize()
+        q.put((rank, ok))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
+    world = min(torch.cuda.device_count(), 8)
+    if world < 2:
+        # one GPU: the sharded layer must degenerate to the plain path
+        import onebitsparsemul_b200 as ob
+        rng = np.random.default_rng(10)
+        dense, scale = helpers.make_weights(rng, 512, 256)
+        w = torch.from_numpy(dense).cuda()
+        layer = ShardedBinaryLinear(512, 256).pack_full(w)
+        B = torch.from_numpy(helpers.make_tokens(rng, 256, 32)).cuda()
+        want = ob.matmul_packed(ob.pack_weight(w), B, out_dtype=torch.float16)
+        for mode in ("none", "all", "overlap"):
+            assert (layer.forward(B, gather=mode) == want).all()
+        return
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in results), results
