@@ -25,6 +25,7 @@
 
 #include "formats.h"
 #include "kernels.h"
+#include "sm100_ptx.h"
 
 namespace {
 
@@ -52,8 +53,10 @@ template <int MS, int BN, int NXG, bool AT> struct Cfg {
   static constexpr int kECols = MS * 8;                    // per weight tile two 4-column metadata slots
   static constexpr int kASlotCols = MS * 32;               // TMEM form: 64 fp16 per row and weight tile
   static constexpr int kASlotsFit = AT ? (512 - kAccCols - kECols) / kASlotCols : 0;
-  // ring of +-1 operand slots: the stages themselves (smem form) or up to 4 TMEM slots
-  static constexpr int kASlots = AT ? (kASlotsFit > 4 ? 4 : kASlotsFit) : kStages;
+  // ring of +-1 operand slots: the stages themselves (smem form), or TMEM slots -- one per stage if
+  // tensor memory has room (then "stage empty" frees both), else a shorter ring of their own
+  static constexpr int kASlots = AT ? (kASlotsFit >= kStages ? kStages : kASlotsFit) : kStages;
+  static constexpr bool kOwnSlotRing = AT && (kASlots != kStages);
   static constexpr int kUsedCols = kAccCols + kECols + (AT ? kASlots * kASlotCols : 0);
   static constexpr int kTmemCols = kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment*/ + 512 /*barriers*/;
@@ -72,123 +75,16 @@ struct PrefillArgs {
   int* status;
 };
 
-// ---- PTX wrappers -----------------------------------------------------------------------------
+using namespace ob_ptx;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait. `budget` is this thread's remaining patience in SM clock cycles; once a wait has
-// run out the thread stops waiting for anything (budget 0), records `code` and lets the kernel
-// drain. The clock is read only every 64 polls: the poll itself is the hot path.
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, long long& budget, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return;
-  if (budget == 0) return;
-  const long long start = clock64();
-  unsigned polls = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++polls & 63u) == 0 && clock64() - start > budget) {
-      budget = 0;
-      atomicCAS(status, 0, code);
-      return;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_alloc(uint32_t smem_dst, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tcgen05_mma_sp_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t e_tmem,
-                                                   uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the same MMA with the compressed +-1 operand read from tensor memory (lane = row, two fp16 per column)
-__device__ __forceinline__ void tcgen05_mma_sp_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t e_tmem,
-                                                      uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], [%1], %2, [%3], %4, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(e_tmem), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tcgen05_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// shared-memory matrix descriptors (sm_100 format: version 1 at bit 46, layout type at bits 61-63)
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
-}
-constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2;
-
-__device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
-  return ((w << (15 - j)) & 0x80008000u) ^ 0xBC00BC00u;
-}
+// Timeline instrumentation for tuning, compiled in only with -DOB_TRACE: one CTA in the middle of the
+// grid records the SM clock at every hand-over of the pipeline.
+#ifdef OB_TRACE
+__device__ long long g_trace[8][512];
+#define OB_TRACE_EV(ev, it) do { if (blockIdx.x == 5 && blockIdx.y == 7 && (it) < 512) g_trace[ev][it] = clock64(); } while (0)
+#else
+#define OB_TRACE_EV(ev, it) do { } while (0)
+#endif
 
 // ---- the kernel -------------------------------------------------------------------------------
 
@@ -227,6 +123,7 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
   }
+  if (threadIdx.x == 0) OB_TRACE_EV(7, 2);
   if (warp == 1) tcgen05_alloc(tmem_slot, C::kTmemCols);
   tcgen05_fence_before();
   __syncthreads();
@@ -242,6 +139,7 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
       for (int it = 0; it < kt; ++it) {
         const int s = it % C::kStages;
         mbar_wait(bar_empty(s), ((it / C::kStages) & 1) ^ 1, budget, a.status, 1);
+        OB_TRACE_EV(0, it);
         mbar_expect_tx(bar_full(s), C::kTxBytes);
 #pragma unroll
         for (int j = 0; j < BN / 64; ++j)
@@ -261,8 +159,9 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       for (int it = 0; it < kt; ++it) {
         const int s = it % C::kStages, x = it % C::kASlots;
-        mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 2);
+        // "operand full" covers "TMA landed": every expander thread waited for the stage first
         mbar_wait(bar_afull(x), (it / C::kASlots) & 1, budget, a.status, 3);
+        OB_TRACE_EV(5, it);
         tcgen05_fence_after();
         const uint64_t bdesc = make_desc(stage_b(s), C::kBBoxBytes, 1024, kLayoutSw128);
 #pragma unroll
@@ -283,7 +182,8 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
           }
         }
         tcgen05_commit(bar_empty(s));
-        if constexpr (AT) tcgen05_commit(bar_aempty(x));
+        if constexpr (C::kOwnSlotRing) tcgen05_commit(bar_aempty(x));
+        OB_TRACE_EV(6, it);
       }
       tcgen05_commit(bar_acc);
     }
@@ -296,7 +196,9 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
       // every group passes every phase of the barriers it ever waits on (parity tracking)
       const int s = it % C::kStages, x = it % C::kASlots;
       mbar_wait(bar_full(s), (it / C::kStages) & 1, budget, a.status, 4);
-      if constexpr (AT) mbar_wait(bar_aempty(x), ((it / C::kASlots) & 1) ^ 1, budget, a.status, 6);
+      if (threadIdx.x == 64) OB_TRACE_EV(1, it);
+      if constexpr (C::kOwnSlotRing) mbar_wait(bar_aempty(x), ((it / C::kASlots) & 1) ^ 1, budget, a.status, 6);
+      if (threadIdx.x == 64) OB_TRACE_EV(2, it);
 #pragma unroll
       for (int t = 0; t < MS; ++t) {
         if ((it * MS + t) % NXG != xg) continue;
@@ -324,11 +226,13 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
         }
         mbar_arrive(bar_afull(x));
       }
+      if (threadIdx.x == 64) OB_TRACE_EV(3, it);
     }
   } else {
     // ---------------- epilogue: warp quadrant = warp % 4, thread = output row ----------------
     const int q = warp & 3;
     mbar_wait(bar_acc, 0, budget, a.status, 5);
+    if (q == 0 && lane == 0) OB_TRACE_EV(7, 0);
     tcgen05_fence_after();
 #pragma unroll 1
     for (int t = 0; t < MS; ++t) {
@@ -369,6 +273,7 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
       }
     }
     tcgen05_fence_before();
+    if (q == 0 && lane == 0) OB_TRACE_EV(7, 1);
   }
 
   __syncthreads();
@@ -376,6 +281,7 @@ ob_gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmap_b, PrefillArgs a
     tcgen05_fence_after();
     tcgen05_dealloc(tmem_base, C::kTmemCols);
   }
+  if (threadIdx.x == 0) OB_TRACE_EV(7, 3);
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -416,6 +322,11 @@ cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t s
 
 namespace ob {
 
+bool prefill2_supported(int64_t m, int64_t n, int64_t k);
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, int ks, const void* bits_tile, const void* meta_tile,
+                                 const void* scale, void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                 cudaStream_t stream);
+
 bool prefill_supported(int64_t m, int64_t n, int64_t k) {
   return m % BM == 0 && k % BK == 0 && n % 8 == 0 && n >= 8 && k >= BK;
 }
@@ -426,20 +337,35 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return cudaErrorNotSupported;
   if ((reinterpret_cast<uintptr_t>(b) & 15) != 0) return cudaErrorMisalignedAddress;
+  // tensor map of B (k x n row-major): boxes of 64 tokens x box_rows k-rows, 128-byte swizzle
+  auto make_map = [&](CUtensorMap* tmap, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)k};
+    const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode(tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  };
+  // Tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <AT><MS><BN/64><NXG> picks a single-CTA
+  // variant; 2 / 22 = CTA-pair kernel with one / two weight tiles per stage; 1 = shape heuristic
+  // without the CTA-pair kernel.
+  static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
+  const int64_t row_tiles = m / BM;
+  const bool two = (m % 256 == 0);
+  // The CTA-pair kernel (256 rows x 256 tokens per pair, each CTA staging half of the token tile) is
+  // the fastest once its pairs fill the 74 SM pairs.
+  const bool pair_fits = n > 128 && prefill2_supported(m, n, k) && (row_tiles / 2) * ((n + 255) / 256) >= 74;
+  if (((forced == 2 || forced == 22) && prefill2_supported(m, n, k)) || (forced == 0 && pair_fits)) {
+    const int ks = (forced == 2) ? 1 : 2;
+    CUtensorMap tmap2;
+    if (!make_map(&tmap2, BK * ks)) return cudaErrorInvalidValue;
+    return launch_gemm_prefill2(&tmap2, ks, bits_tile, meta_tile, scale, d, m, n, k, out_type, status, stream);
+  }
   CUtensorMap tmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)k};
-  const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
-  const cuuint32_t box[2] = {64, (cuuint32_t)BK};
-  const cuuint32_t estr[2] = {1, 1};
-  if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr,
-             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return cudaErrorInvalidValue;
+  if (!make_map(&tmap, BK)) return cudaErrorInvalidValue;
   PrefillArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                 static_cast<const __half*>(scale), d, m, n, k, out_type, status};
-  // tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <AT><MS><BN/64><NXG>
-  static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
-  const bool two = (m % 256 == 0);
   switch (forced) {
     case 121: return launch<1, 128, 1, false>(tmap, a, stream);
     case 141: return launch<1, 256, 1, false>(tmap, a, stream);
@@ -452,13 +378,18 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
     case 1222: if (two) return launch<2, 128, 2, true>(tmap, a, stream); break;
     default: break;
   }
-  // Shape heuristic. All default variants keep the +-1 operand in tensor memory. A 256-token tile
-  // halves the weight-side work per token and is the fastest once it fills the 148 SMs; otherwise
-  // two stacked weight tiles share a 128-token tile, or the smallest tile spreads a small problem.
-  const int64_t row_tiles = m / BM;
+  // Single-CTA variants, all with the +-1 operand in tensor memory: a 256-token tile once it fills
+  // the 148 SMs, else two stacked weight tiles sharing 128 tokens, else the smallest tile, which
+  // spreads a small problem over the most SMs.
   if (n > 128 && row_tiles * ((n + 255) / 256) >= 148) return launch<1, 256, 1, true>(tmap, a, stream);
   if (two && (row_tiles / 2) * ((n + 127) / 128) >= 148) return launch<2, 128, 1, true>(tmap, a, stream);
   return launch<1, 128, 1, true>(tmap, a, stream);
 }
 
 }  // namespace ob
+
+#ifdef OB_TRACE
+extern "C" int onebit_debug_read_trace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 8 * 512);
+}
+#endif
