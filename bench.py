@@ -65,7 +65,7 @@ class ClockSampler:
                     self.samples.append(parts)
             except Exception:
                 pass
-            self.stop.wait(0.1)
+            self.stop.wait(0.02)
 
     def __enter__(self):
         self.thread.start()
@@ -123,6 +123,44 @@ def run_reference(args):
             "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def decode_extras(ob, lib, _lib, dev):
+    """The memory-bound regime of the same path (config 2: 7B-class layers, few tokens): algorithmic
+    HBM GB/s of the decode kernel, launched back to back over a pool of distinct packed weights
+    larger than L2 so that every call streams its weights from HBM."""
+    import torch
+    peaks = load_peaks()
+    out = []
+    for (m, k, n) in ((4096, 4096, 1), (11008, 4096, 1), (4096, 11008, 16)):
+        w = torch.zeros((m, k // 4, 4), dtype=torch.float16, device=dev)
+        w[..., 0], w[..., 3] = 1.0, -1.0
+        pw = ob.pack_weight(w.reshape(m, k), apply_mask=False, keep_reference=False)
+        del w
+        weight_bytes = pw.bits_tile.numel() + pw.meta_tile.numel()
+        copies = max(2, int(2.2 * 126e6 / weight_bytes))
+        pool = [ob.PackedWeight(m, k, pw.bits_tile.clone(), pw.meta_tile.clone(), None) for _ in range(copies)]
+        B = torch.randn((k, n), device=dev, dtype=torch.float32).to(torch.float16)
+        C = torch.empty((m, n), dtype=torch.float16, device=dev)
+        for i in range(copies):
+            ob.matmul_packed(pool[i], B, out=C, kernel=_lib.KERNEL_DECODE)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        calls = 4 * copies
+        e0.record()
+        for i in range(calls):
+            ob.matmul_packed(pool[i % copies], B, out=C, kernel=_lib.KERNEL_DECODE)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / calls
+        alg = weight_bytes + 2 * k * n + 2 * m * n
+        out.append({"a_rows": m, "a_cols": k, "n": n, "us_per_call": us, "algorithmic_bytes": alg,
+                    "gbs": alg / us / 1e3, "frac_of_measured_hbm": alg / us / 1e3 / peaks["hbm_gbs"],
+                    "weight_pool_mb": copies * weight_bytes / 1e6})
+        del pool
+    return {"kernel": "ob_gemm_decode_kernel", "bound": "hbm", "peak_gbs": peaks["hbm_gbs"], "cases": out,
+            "note": "back-to-back launches over a weight pool > 2 x L2; a single call moves 3-9 MB, so launch and "
+                    "DRAM latency, not bandwidth, set its time"}
 
 
 def run_ours(args):
@@ -218,6 +256,10 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops_step * e2e_steps / (float(t.item()) * 1e-3) / 1e12
 
+    decode = None
+    if rank == 0 and world == 1 and not args.no_decode:
+        decode = decode_extras(ob, lib, _lib, dev)
+
     if rank == 0:
         peaks = load_peaks()
         sparse_peak = 2.0 * peaks["bf16_tflops"]
@@ -247,6 +289,8 @@ def run_ours(args):
                              "sample": f"2048 of {S} weight rows x full k x full n ({cpu_dt:.2f} s)"},
             "clocks": clocks.summary(),
         }
+        if decode is not None:
+            line["decode"] = decode
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -259,6 +303,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--no-decode", action="store_true", help="skip the supplementary decode-regime numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

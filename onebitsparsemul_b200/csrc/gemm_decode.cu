@@ -2,17 +2,20 @@
 // from HBM exactly once and is meant to be bound by that stream, not by arithmetic.
 //
 // Replaces the reference's 128x64x128 CUTLASS threadblock (csrc/kernel.h:23-25) for the shapes
-// where its 64-wide token tile is almost empty. Design:
-//   * one CTA = one 128-row block of A x one slice of K; 8 warps, warp w owns rows 16w..16w+15;
-//   * the K slices of one row block form a thread-block cluster (split-K). Partial sums are
-//     reduced through distributed shared memory in a fixed order: deterministic, no atomics, no
-//     scratch memory in HBM;
-//   * every warp issues the loads of all its tiles of a chunk up front (16 B metadata + 16 B sign
-//     words per lane and tile) so that a whole matrix of a few MiB is in flight at once;
+// where its 64-wide token tile is almost empty. Such a call moves only a few MiB, so the kernel is
+// built to be short: every weight load of a warp is issued before anything else, and there is one
+// cluster-wide synchronisation in its whole life.
+//   * one CTA = one 128-row block of A x one slice of K, 16 warps: warp w owns rows 16(w%8)..+15 of
+//     half (w/8) of the slice, so a cluster of S CTAs cuts K into 2S slices;
 //   * the 2:4 gather is done by the tensor core: sign words are expanded in registers to fp16 +-1
 //     pairs (one shift + one logic op per pair, see the tile order in formats.h) and fed with the
 //     metadata words to mma.sp m16n8k32 with fp32 accumulation;
-//   * tokens (B, k x n row-major) are staged transposed in shared memory, zero-padded to 8 or 16.
+//   * tokens (B, k x n row-major) are staged row-major in shared memory, zero-padded to 8 or 16 per
+//     row, by the half that uses them (named barrier per half);
+//   * split-K reduction: every warp PUSHES its partial sums through distributed shared memory into
+//     the CTA that owns those output rows; after the single cluster barrier each CTA sums its 2S
+//     slices in a fixed order from its own shared memory, scales, converts and stores. No atomics,
+//     no scratch in HBM, no remote reads, deterministic.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -24,9 +27,17 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kChunkTiles = 4;                       // tiles (128 k each) whose loads are in flight together
+// Timeline instrumentation for tuning, compiled in only with -DOB_TRACE.
+#ifdef OB_TRACE
+__device__ long long g_trace_dec[4][16];
+#define OB_TRACE_EV(ev) do { if (blockIdx.x == 3 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == 511) && blockIdx.y < 2) g_trace_dec[blockIdx.y * 2 + (threadIdx.x != 0)][ev] = clock64(); } while (0)
+#else
+#define OB_TRACE_EV(ev) do { } while (0)
+#endif
+
+constexpr int kChunkTiles = 4;                       // tiles (128 k each) of one warp in flight together
 constexpr int kChunkK = kChunkTiles * OB_TILE_K;     // 512
-constexpr int kBtStride = kChunkK + 8;               // halves; +8 skews rows over the banks
+constexpr int kMaxSlices = 16;                       // 2 halves x cluster of up to 8
 
 __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
   // bits j and 16+j of w -> fp16x2 {bit ? +1 : -1}
@@ -53,6 +64,9 @@ __device__ __forceinline__ uint2 ld_stream8(const void* p) {
   asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
   return v;
 }
+__device__ __forceinline__ void half_barrier(int half) {      // the 256 threads of one half of the CTA
+  asm volatile("bar.sync %0, 256;" ::"r"(half + 1) : "memory");
+}
 
 struct DecodeArgs {
   const uint8_t* bits_tile;
@@ -65,21 +79,45 @@ struct DecodeArgs {
 
 // NT = number of 8-token tiles per pass (1 or 2)
 template <int NT, typename OutT>
-__global__ void __launch_bounds__(256) ob_gemm_decode_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
   constexpr int NP = NT * 8;
-  __shared__ __align__(16) __half s_bt[NP * kBtStride];
-  __shared__ __align__(16) float s_part[128 * NP];
+  __shared__ __align__(16) __half s_b[2][kChunkK * NP];           // per half: s_b[kk][j] = B[k0 + kk][n0 + j]
+  __shared__ __align__(16) float s_recv[kMaxSlices * 16 * NP];    // [slice][row of this CTA's share][token]
 
+  OB_TRACE_EV(0);
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks();
   const int rank = (int)cluster.block_rank();
   const int64_t mb = blockIdx.x;
   const int64_t n0 = (int64_t)blockIdx.z * NP;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int half = warp >> 3, w8 = warp & 7;                  // K half, 16-row block
+  const int tid_h = threadIdx.x & 255;                        // thread index inside the half
   const int g = lane >> 2, t = lane & 3;
 
   const int64_t tiles_k = a.k / OB_TILE_K;
-  const int64_t tile_begin = tiles_k * rank / S, tile_end = tiles_k * (rank + 1) / S;
+  const int slices = 2 * S, slice = 2 * rank + half;
+  const int64_t tile_begin = tiles_k * slice / slices, tile_end = tiles_k * (slice + 1) / slices;
+
+  const int u = g + 8 * (t & 1) + 16 * w8;                    // metadata lane of this thread
+  const int row_lo = 16 * w8 + g;
+
+  // 1. the weight loads of the first chunk, before anything else
+  uint4 meta[kChunkTiles];
+  uint2 blo[kChunkTiles], bhi[kChunkTiles];
+  auto load_chunk = [&](int64_t chunk) {
+#pragma unroll
+    for (int ti = 0; ti < kChunkTiles; ++ti) {
+      if (chunk + ti < tile_end) {
+        const int64_t tile = mb * tiles_k + chunk + ti;
+        meta[ti] = ld_stream16(a.meta_tile + tile * OB_TILE_META_BYTES + u * 16);
+        blo[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + row_lo * 8);
+        bhi[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + (row_lo + 8) * 8);
+      }
+    }
+  };
+  load_chunk(tile_begin);
+  OB_TRACE_EV(1);
 
   float acc[NT][4];
 #pragma unroll
@@ -87,35 +125,38 @@ __global__ void __launch_bounds__(256) ob_gemm_decode_kernel(DecodeArgs a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
 
-  const int u = g + 8 * (t & 1) + 16 * warp;                 // metadata lane of this thread
-  const int row_lo = 16 * warp + g;
+  const int nvalid = (int)min((int64_t)NP, a.n - n0);
+  const bool vec_rows = (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
+  __half* sb = s_b[half];
 
   for (int64_t chunk = tile_begin; chunk < tile_end; chunk += kChunkTiles) {
     const int ntile = (int)min((int64_t)kChunkTiles, tile_end - chunk);
-
-    // 1. all weight loads of the chunk
-    uint4 meta[kChunkTiles];
-    uint2 blo[kChunkTiles], bhi[kChunkTiles];
-#pragma unroll
-    for (int ti = 0; ti < kChunkTiles; ++ti) {
-      if (ti < ntile) {
-        const int64_t tile = mb * tiles_k + chunk + ti;
-        meta[ti] = ld_stream16(a.meta_tile + tile * OB_TILE_META_BYTES + u * 16);
-        blo[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + row_lo * 8);
-        bhi[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + (row_lo + 8) * 8);
-      }
+    if (chunk != tile_begin) {
+      half_barrier(half);                                     // previous chunk's readers are done
+      load_chunk(chunk);
     }
-
-    // 2. tokens of the chunk, transposed: s_bt[j][kk] = B[k0 + kk][n0 + j]
+    // 2. tokens of the chunk: sb[kk][j] = B[k0 + kk][n0 + j], zero beyond n
     const int64_t k0 = chunk * OB_TILE_K;
     const int kc = ntile * OB_TILE_K;
-    __syncthreads();                                          // previous chunk's readers are done
-    for (int idx = threadIdx.x; idx < kc * NP; idx += 256) {
-      const int kk = idx / NP, j = idx % NP;
-      const __half v = (n0 + j < a.n) ? a.b[(k0 + kk) * a.n + n0 + j] : __float2half(0.f);
-      s_bt[j * kBtStride + kk] = v;
+    if (vec_rows) {
+      constexpr int kPieces = NP / 8;                         // 16-byte pieces per token row
+      for (int idx = tid_h; idx < kc * kPieces; idx += 256) {
+        const int kk = idx / kPieces, pc = idx % kPieces;
+        *reinterpret_cast<uint4*>(&sb[kk * NP + pc * 8]) =
+            __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
+      }
+    } else {
+      for (int kk = tid_h; kk < kc; kk += 256) {
+        __align__(16) __half row[NP];
+#pragma unroll
+        for (int j = 0; j < NP; ++j) row[j] = (j < nvalid) ? a.b[(k0 + kk) * a.n + n0 + j] : __float2half(0.f);
+#pragma unroll
+        for (int p = 0; p < NP / 8; ++p) *reinterpret_cast<uint4*>(&sb[kk * NP + p * 8]) = *reinterpret_cast<uint4*>(&row[p * 8]);
+      }
     }
-    __syncthreads();
+    OB_TRACE_EV(2);
+    half_barrier(half);
+    OB_TRACE_EV(3);
 
     // 3. four mma.sp per tile and token tile
 #pragma unroll
@@ -133,10 +174,12 @@ __global__ void __launch_bounds__(256) ob_gemm_decode_kernel(DecodeArgs a) {
           af[3] = expand_pair(wh[kb >> 1], j2);
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            const uint32_t* brow = reinterpret_cast<const uint32_t*>(s_bt + (nt * 8 + g) * kBtStride + ti * OB_TILE_K + kb * 32);
+            // fragment register i: token column nt*8+g, k rows 2t+8i and 2t+8i+1 of the k-block
+            const unsigned short* bcol = reinterpret_cast<const unsigned short*>(sb) + (ti * OB_TILE_K + kb * 32 + 2 * t) * NP + nt * 8 + g;
             uint32_t bf[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) bf[i] = brow[t + 4 * i];
+            for (int i = 0; i < 4; ++i)
+              bf[i] = (uint32_t)bcol[(8 * i) * NP] | ((uint32_t)bcol[(8 * i + 1) * NP] << 16);
             mma_sp_16832(acc[nt], af, bf, mw[kb]);
           }
         }
@@ -144,35 +187,41 @@ __global__ void __launch_bounds__(256) ob_gemm_decode_kernel(DecodeArgs a) {
     }
   }
 
-  // split-K reduction through distributed shared memory, fixed order
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    s_part[row_lo * NP + nt * 8 + 2 * t] = acc[nt][0];
-    s_part[row_lo * NP + nt * 8 + 2 * t + 1] = acc[nt][1];
-    s_part[(row_lo + 8) * NP + nt * 8 + 2 * t] = acc[nt][2];
-    s_part[(row_lo + 8) * NP + nt * 8 + 2 * t + 1] = acc[nt][3];
-  }
-  cluster.sync();
+  OB_TRACE_EV(4);
+  // 4. push the partial sums to the CTA that owns the rows: CTA r owns rows [r * 128/S, (r+1) * 128/S)
   const int rows_per = 128 / S;
-  for (int e = threadIdx.x; e < rows_per * NP; e += 256) {
-    const int r = rank * rows_per + e / NP, j = e % NP;
+#pragma unroll
+  for (int hrow = 0; hrow < 2; ++hrow) {
+    const int r = row_lo + 8 * hrow;
+    float* dst = cluster.map_shared_rank(s_recv, r / rows_per) + (slice * rows_per + (r % rows_per)) * NP;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+      *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(acc[nt][2 * hrow], acc[nt][2 * hrow + 1]);
+  }
+  OB_TRACE_EV(5);
+  cluster.sync();                                             // the only cluster-wide barrier
+  OB_TRACE_EV(6);
+
+  // 5. fixed-order sum of the 2S slices from this CTA's own shared memory
+  for (int e = threadIdx.x; e < rows_per * NP; e += 512) {
+    const int rr = e / NP, j = e % NP;
     float sum = 0.f;
-    for (int s = 0; s < S; ++s) sum += cluster.map_shared_rank(s_part, s)[r * NP + j];
-    const int64_t row = mb * 128 + r;
+    for (int sl = 0; sl < slices; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
+    const int64_t row = mb * 128 + rank * rows_per + rr;
     if (a.scale) sum *= __half2float(a.scale[row]);
-    if (n0 + j < a.n) {
+    if (j < nvalid) {
       if constexpr (sizeof(OutT) == 2) static_cast<__half*>(a.d)[row * a.n + n0 + j] = __float2half_rn(sum);
       else static_cast<float*>(a.d)[row * a.n + n0 + j] = sum;
     }
   }
-  cluster.sync();                                             // keep s_part alive until every peer has read it
+  OB_TRACE_EV(7);
 }
 
 template <int NT, typename OutT>
 cudaError_t launch(const DecodeArgs& a, int S, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(a.m / 128), (unsigned)S, (unsigned)((a.n + NT * 8 - 1) / (NT * 8)));
-  cfg.blockDim = dim3(256);
+  cfg.blockDim = dim3(512);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -193,14 +242,20 @@ cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, con
                                void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream) {
   DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                static_cast<const __half*>(scale), static_cast<const __half*>(b), d, m, n, k};
-  // split K over a cluster of up to 8 CTAs, as far as there are tiles and until the grid holds
-  // about four CTAs per SM
+  // split K over a cluster of up to 8 CTAs (16 slices), as far as there are tiles and until the
+  // grid holds about two CTAs per SM
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
   int S = 1;
-  while (S < 8 && 2 * S <= tiles_k && row_blocks * S < 4 * 148) S *= 2;
+  while (S < 8 && 4 * S <= tiles_k && row_blocks * S < 2 * 148) S *= 2;
   const bool two = (n > 8);
   if (out_type == OB_OUT_F16) return two ? launch<2, __half>(a, S, stream) : launch<1, __half>(a, S, stream);
   return two ? launch<2, float>(a, S, stream) : launch<1, float>(a, S, stream);
 }
 
 }  // namespace ob
+
+#ifdef OB_TRACE
+extern "C" int onebit_debug_read_trace_decode(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace_dec, sizeof(long long) * 4 * 16);
+}
+#endif

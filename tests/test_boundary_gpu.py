@@ -1,0 +1,86 @@
+"""The other reference-facing surfaces on the GPU: the `onebit_sparse_cuda` torch extension (both
+argument orders the reference uses), the drop-in `onebit_sparse_mul` import name, and the `a.out`
+CLI with the reference's flags and output lines."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def problem():
+    rng = np.random.default_rng(77)
+    m, k, n = 256, 512, 40
+    dense, scale = helpers.make_weights(rng, m, k)
+    canon, signs, _ = oracle.compress(dense)
+    bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, oracle.META_PYTHON)
+    B = helpers.make_tokens(rng, k, n, "int")
+    want, _ = oracle.gemm(bits, meta, oracle.META_PYTHON, B, m)
+    want_scaled, _ = oracle.gemm(bits, meta, oracle.META_PYTHON, B, m, scale=scale)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return dict(m=m, k=k, n=n, A=t(bits), meta=t(meta.view(np.int16)), B=t(B), scale=t(scale), want=want, want_scaled=want_scaled)
+
+
+def test_torch_extension_both_argument_orders(problem):
+    from onebitsparsemul_b200 import build
+    build.build_torch_extension()
+    import onebit_sparse_cuda
+    p = problem
+    C = torch.zeros((p["m"], p["n"]), dtype=torch.float32, device="cuda")
+    onebit_sparse_cuda.onebit_mul(p["A"], p["B"], p["meta"], C)              # the reference's C++ order
+    assert (C.cpu().numpy() == p["want"]).all()
+    C.zero_()
+    onebit_sparse_cuda.onebit_mul(p["A"], p["B"], C, p["meta"])              # the reference's Python order
+    assert (C.cpu().numpy() == p["want"]).all()
+    C16 = torch.zeros((p["m"], p["n"]), dtype=torch.float16, device="cuda")
+    onebit_sparse_cuda.onebit_mul(p["A"], p["B"], p["meta"], C16, p["scale"])
+    ok, worst = helpers.row_tolerance_ok(C16.cpu().numpy(), p["want_scaled"])
+    assert ok, worst
+    with pytest.raises(RuntimeError):
+        onebit_sparse_cuda.onebit_mul(p["A"], p["B"], p["meta"], torch.zeros((p["m"], p["n"] + 1), device="cuda"))
+    with pytest.raises(RuntimeError):
+        onebit_sparse_cuda.onebit_mul(p["A"], p["B"].cpu(), p["meta"], C)
+
+
+def test_reference_import_name(problem):
+    import onebit_sparse_mul as ref_name
+    p = problem
+    C = ref_name.cuda_binary_mul(p["A"], p["B"], p["meta"])
+    assert C.dtype == torch.float32 and C.is_cuda and (C.cpu().numpy() == p["want"]).all()
+    C2 = torch.empty_like(C)
+    assert ref_name.cuda_binary_mul_(p["A"], p["B"], C2, p["meta"]) is C2 and (C2 == C).all()
+    layer = ref_name.BinaryLinear_2_4(128, 128)
+    assert layer.vaild is False and tuple(layer.packed_binary_sparse.shape) == (64, 16) and tuple(layer.meta.shape) == (128, 8)
+
+
+def run_cli(*args):
+    exe = os.path.join(ROOT, "a.out")
+    if not os.path.exists(exe):
+        from onebitsparsemul_b200 import build
+        build.build_cli()
+    return subprocess.run([exe, *args], capture_output=True, text=True, timeout=300)
+
+
+def test_cli_reference_flags_and_output_lines():
+    r = run_cli("--a_rows=512", "--n=512", "--a_cols=512", "--reference-check=true", "--iterations=5",
+                "--alpha=1", "--beta=0", "--a_ell_num_columns=512", "--a_ell_blocksize=16", "--a_base=0")
+    lines = r.stdout.strip().splitlines()
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert re.fullmatch(r"Runtime: [0-9.e+-]+ ms", lines[0]) and re.fullmatch(r" GFLOPs: [0-9.e+-]+", lines[1])
+    assert lines[2] == "Passed"
+    # the reference's degenerate fill through the reference's own entry point, exact check
+    r = run_cli("--a_rows=256", "--n=64", "--a_cols=256", "--dist=reference", "--stateless=true", "--reference-check=true", "--iterations=2")
+    assert r.returncode == 0 and r.stdout.strip().endswith("Passed")
+    # decode shape, fp16 output with scale, JSON mode
+    r = run_cli("--a_rows=4096", "--n=4", "--a_cols=4096", "--out=fp16", "--scale=true", "--reference-check=true", "--json")
+    assert r.returncode == 0 and '"passed": true' in r.stdout
+    assert "--a_rows" in run_cli("--help").stdout
