@@ -10,8 +10,9 @@
 //   * the 2:4 gather is done by the tensor core: sign words are expanded in registers to fp16 +-1
 //     pairs (one shift + one logic op per pair, see the tile order in formats.h) and fed with the
 //     metadata words to mma.sp m16n8k32 with fp32 accumulation;
-//   * tokens (B, k x n row-major) are staged row-major in shared memory, zero-padded to 8 or 16 per
-//     row, by the half that uses them (named barrier per half);
+//   * tokens (B, k x n row-major) are staged TRANSPOSED in shared memory (one padded row per token,
+//     zero rows beyond n) by the half that uses them (named barrier per half), so that a B fragment
+//     register is one 32-bit load;
 //   * split-K reduction: every warp PUSHES its partial sums through distributed shared memory into
 //     the CTA that owns those output rows; after the single cluster barrier each CTA sums its 2S
 //     slices in a fixed order from its own shared memory, scales, converts and stores. No atomics,
@@ -19,6 +20,8 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <cstdlib>
 
 #include "formats.h"
 #include "kernels.h"
@@ -35,9 +38,10 @@ __device__ long long g_trace_dec[4][16];
 #define OB_TRACE_EV(ev) do { } while (0)
 #endif
 
-constexpr int kChunkTiles = 4;                       // tiles (128 k each) of one warp in flight together
-constexpr int kChunkK = kChunkTiles * OB_TILE_K;     // 512
+constexpr int kChunkTiles = 3;                       // tiles (128 k each) of one warp in flight together
+constexpr int kChunkK = kChunkTiles * OB_TILE_K;     // 384
 constexpr int kMaxSlices = 16;                       // 2 halves x cluster of up to 8
+constexpr int kBtStride = kChunkK + 8;               // halves per token column; +8 skews the columns over the banks
 
 __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
   // bits j and 16+j of w -> fp16x2 {bit ? +1 : -1}
@@ -81,13 +85,14 @@ struct DecodeArgs {
 template <int NT, typename OutT>
 __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
   constexpr int NP = NT * 8;
-  __shared__ __align__(16) __half s_b[2][kChunkK * NP];           // per half: s_b[kk][j] = B[k0 + kk][n0 + j]
+  __shared__ __align__(16) __half s_b[2][NP * kBtStride];          // per half: s_b[j][kk] = B[k0 + kk][n0 + j]
   __shared__ __align__(16) float s_recv[kMaxSlices * 16 * NP];    // [slice][row of this CTA's share][token]
 
   OB_TRACE_EV(0);
-  cg::cluster_group cluster = cg::this_cluster();
-  const int S = (int)cluster.num_blocks();
-  const int rank = (int)cluster.block_rank();
+  // the cluster spans the whole y extent of the grid: rank and size come from the launch geometry,
+  // which is cheaper to read at kernel start than the cluster special registers
+  const int S = (int)gridDim.y;
+  const int rank = (int)blockIdx.y;
   const int64_t mb = blockIdx.x;
   const int64_t n0 = (int64_t)blockIdx.z * NP;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,11 +124,15 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
   load_chunk(tile_begin);
   OB_TRACE_EV(1);
 
-  float acc[NT][4];
+  // two independent accumulation chains per token tile (even / odd k-blocks): the warp-level MMA has
+  // a long latency and a single chain would serialise on it
+  float acc[2][NT][4];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
+  for (int c = 0; c < 2; ++c)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[c][nt][i] = 0.f;
 
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
   const bool vec_rows = (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
@@ -142,16 +151,15 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
       constexpr int kPieces = NP / 8;                         // 16-byte pieces per token row
       for (int idx = tid_h; idx < kc * kPieces; idx += 256) {
         const int kk = idx / kPieces, pc = idx % kPieces;
-        *reinterpret_cast<uint4*>(&sb[kk * NP + pc * 8]) =
-            __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
+        const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) sb[(pc * 8 + jj) * kBtStride + kk] = h[jj];
       }
     } else {
       for (int kk = tid_h; kk < kc; kk += 256) {
-        __align__(16) __half row[NP];
 #pragma unroll
-        for (int j = 0; j < NP; ++j) row[j] = (j < nvalid) ? a.b[(k0 + kk) * a.n + n0 + j] : __float2half(0.f);
-#pragma unroll
-        for (int p = 0; p < NP / 8; ++p) *reinterpret_cast<uint4*>(&sb[kk * NP + p * 8]) = *reinterpret_cast<uint4*>(&row[p * 8]);
+        for (int j = 0; j < NP; ++j) sb[j * kBtStride + kk] = (j < nvalid) ? a.b[(k0 + kk) * a.n + n0 + j] : __float2half(0.f);
       }
     }
     OB_TRACE_EV(2);
@@ -175,12 +183,11 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
             // fragment register i: token column nt*8+g, k rows 2t+8i and 2t+8i+1 of the k-block
-            const unsigned short* bcol = reinterpret_cast<const unsigned short*>(sb) + (ti * OB_TILE_K + kb * 32 + 2 * t) * NP + nt * 8 + g;
+            const uint32_t* brow = reinterpret_cast<const uint32_t*>(sb + (nt * 8 + g) * kBtStride + ti * OB_TILE_K + kb * 32);
             uint32_t bf[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              bf[i] = (uint32_t)bcol[(8 * i) * NP] | ((uint32_t)bcol[(8 * i + 1) * NP] << 16);
-            mma_sp_16832(acc[nt], af, bf, mw[kb]);
+            for (int i = 0; i < 4; ++i) bf[i] = brow[t + 4 * i];
+            mma_sp_16832(acc[kb & 1][nt], af, bf, mw[kb]);
           }
         }
       }
@@ -189,6 +196,7 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
 
   OB_TRACE_EV(4);
   // 4. push the partial sums to the CTA that owns the rows: CTA r owns rows [r * 128/S, (r+1) * 128/S)
+  cg::cluster_group cluster = cg::this_cluster();
   const int rows_per = 128 / S;
 #pragma unroll
   for (int hrow = 0; hrow < 2; ++hrow) {
@@ -196,7 +204,8 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
     float* dst = cluster.map_shared_rank(s_recv, r / rows_per) + (slice * rows_per + (r % rows_per)) * NP;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
-      *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(acc[nt][2 * hrow], acc[nt][2 * hrow + 1]);
+      *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(acc[0][nt][2 * hrow] + acc[1][nt][2 * hrow],
+                                                                   acc[0][nt][2 * hrow + 1] + acc[1][nt][2 * hrow + 1]);
   }
   OB_TRACE_EV(5);
   cluster.sync();                                             // the only cluster-wide barrier
@@ -247,6 +256,9 @@ cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, con
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
   int S = 1;
   while (S < 8 && 4 * S <= tiles_k && row_blocks * S < 2 * 148) S *= 2;
+  // tuning knob for experiments
+  static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_SPLIT"); return v ? atoi(v) : 0; }();
+  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) S = forced;
   const bool two = (n > 8);
   if (out_type == OB_OUT_F16) return two ? launch<2, __half>(a, S, stream) : launch<1, __half>(a, S, stream);
   return two ? launch<2, float>(a, S, stream) : launch<1, float>(a, S, stream);
