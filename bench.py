@@ -291,7 +291,7 @@ def run_ours(args):
                          # this workload (profiles/prefill_kernel_square8192_ncu_full.md); algorithmic bytes are 2.81e8
                          "traffic": 2.518e8 if S == 8192 else None,
                          "peak_note": f"2 x dense bf16 burst peak ({peaks['bf16_tflops']} TFLOP/s, {peaks['source']}): 2:4 sparse MMA rate",
-                         "frac_of_dense_peak": achieved / peaks["bf16_tflops"], "kernel": "ob_gemm_prefill_kernel",
+                         "frac_of_dense_peak": achieved / peaks["bf16_tflops"], "kernel": "ob_gemm_prefill2_kernel<2> (CTA pair)",
                          "kernel_ms": kernel_ms},
             "cpu_baseline": {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                              "sample": f"2048 of {S} weight rows x full k x full n ({cpu_dt:.2f} s)"},

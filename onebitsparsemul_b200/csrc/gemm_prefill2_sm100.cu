@@ -71,11 +71,13 @@ struct Prefill2Args {
   int64_t m, n, k;
   int out_type;
   int* status;
+  int tma_store;     // 1: fp16 output leaves through shared memory and TMA stores (tmap_c is valid)
 };
 
 template <int KS>
 __global__ void __launch_bounds__(Cfg2<KS>::kThreads, 1)
-ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill2Args a) {
+ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
+                        Prefill2Args a) {
   using C = Cfg2<KS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -206,6 +208,39 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill2Args
     const int64_t row = mt * BM + q * 32 + lane;
     const int64_t nbase = (int64_t)blockIdx.y * BN;
     const float sc = a.scale ? __half2float(a.scale[row]) : 1.f;
+    if (a.tma_store) {
+      // fp16 output: the tile is assembled in the (now idle) first pipeline stage as 4 boxes of
+      // 128 rows x 64 tokens with the 128-byte swizzle, then written with 4 TMA stores: full-line
+      // writes, and the threads are done as soon as their rows are in shared memory
+      uint8_t* cbuf = smem_gen + (stage_b(0) - smem_base);
+      const int r = q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+        uint8_t* box_row = cbuf + (c0 >> 6) * (BM * 128) + r * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
+            ow[h] = *reinterpret_cast<const uint32_t*>(&p);
+          }
+          const int chunk = ((c0 & 63) >> 3) + j;              // 16-byte chunk inside the 128-byte box row
+          *reinterpret_cast<uint4*>(box_row + ((chunk ^ (r & 7)) << 4)) = o;
+        }
+      }
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+      if (q == 0 && lane == 0) {
+#pragma unroll
+        for (int bx = 0; bx < BN / 64; ++bx)
+          if (nbase + 64 * bx < a.n) tma_store_2d(&tmap_c, smem_u32(cbuf) + bx * (BM * 128), (int)(nbase + 64 * bx), (int)(mt * BM));
+        tma_store_commit_and_wait();
+      }
+    } else {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 32) {
       uint32_t v[32];
@@ -239,6 +274,7 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill2Args
         }
       }
     }
+    }
     tcgen05_fence_before();
     if (q == 0 && lane == 0) OB_TRACE_EV(7, 1);
   }
@@ -261,7 +297,7 @@ bool prefill2_supported(int64_t m, int64_t n, int64_t k) {
 
 namespace {
 template <int KS>
-cudaError_t launch2(const CUtensorMap& tmap, const Prefill2Args& a, cudaStream_t stream) {
+cudaError_t launch2(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const Prefill2Args& a, cudaStream_t stream) {
   using C = Cfg2<KS>;
   static bool configured[64] = {};
   int dev = 0;
@@ -283,17 +319,20 @@ cudaError_t launch2(const CUtensorMap& tmap, const Prefill2Args& a, cudaStream_t
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill2_kernel<KS>, tmap, a);
+  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill2_kernel<KS>, tmap, tmap_c, a);
 }
 }  // namespace
 
 // tmap: tensor map of B with a box of 64 tokens x (128 * ks) k-rows, 128-byte swizzle
-cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, int ks, const void* bits_tile, const void* meta_tile,
-                                 const void* scale, void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
-                                 cudaStream_t stream) {
+// tmap_c: tensor map of an fp16 C (m x n row-major) with boxes of 64 tokens x 128 rows, 128-byte swizzle,
+//         or NULL (fp32 output, or C not 16-byte aligned): direct stores from registers
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, const void* bits_tile,
+                                 const void* meta_tile, const void* scale, void* d, int64_t m, int64_t n, int64_t k,
+                                 int out_type, int* status, cudaStream_t stream) {
   Prefill2Args a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-                 static_cast<const __half*>(scale), d, m, n, k, out_type, status};
-  return ks == 2 ? launch2<2>(*tmap, a, stream) : launch2<1>(*tmap, a, stream);
+                 static_cast<const __half*>(scale), d, m, n, k, out_type, status, tmap_c != nullptr};
+  const CUtensorMap& tc = tmap_c ? *tmap_c : *tmap;          // unused when tma_store == 0
+  return ks == 2 ? launch2<2>(*tmap, tc, a, stream) : launch2<1>(*tmap, tc, a, stream);
 }
 
 }  // namespace ob

@@ -323,9 +323,9 @@ cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t s
 namespace ob {
 
 bool prefill2_supported(int64_t m, int64_t n, int64_t k);
-cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, int ks, const void* bits_tile, const void* meta_tile,
-                                 const void* scale, void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
-                                 cudaStream_t stream);
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, const void* bits_tile,
+                                 const void* meta_tile, const void* scale, void* d, int64_t m, int64_t n, int64_t k,
+                                 int out_type, int* status, cudaStream_t stream);
 
 bool prefill_supported(int64_t m, int64_t n, int64_t k) {
   return m % BM == 0 && k % BK == 0 && n % 8 == 0 && n >= 8 && k >= BK;
@@ -358,9 +358,20 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   const bool pair_fits = n > 128 && prefill2_supported(m, n, k) && (row_tiles / 2) * ((n + 255) / 256) >= 74;
   if (((forced == 2 || forced == 22) && prefill2_supported(m, n, k)) || (forced == 0 && pair_fits)) {
     const int ks = (forced == 2) ? 1 : 2;
-    CUtensorMap tmap2;
+    CUtensorMap tmap2, tmap_c;
     if (!make_map(&tmap2, BK * ks)) return cudaErrorInvalidValue;
-    return launch_gemm_prefill2(&tmap2, ks, bits_tile, meta_tile, scale, d, m, n, k, out_type, status, stream);
+    // fp16 C leaves through shared memory and TMA stores: boxes of 64 tokens x 128 rows
+    bool c_map = false;
+    if (out_type == OB_OUT_F16 && (reinterpret_cast<uintptr_t>(d) & 15) == 0) {
+      const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)m};
+      const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+      const cuuint32_t box[2] = {64, (cuuint32_t)BM};
+      const cuuint32_t estr[2] = {1, 1};
+      c_map = encode(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    return launch_gemm_prefill2(&tmap2, c_map ? &tmap_c : nullptr, ks, bits_tile, meta_tile, scale, d, m, n, k, out_type,
+                                status, stream);
   }
   CUtensorMap tmap;
   if (!make_map(&tmap, BK)) return cudaErrorInvalidValue;

@@ -125,6 +125,17 @@ __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
 }
 
 
+// TMA store of a shared-memory tile (written by ordinary stores, then fence_proxy_async) to global
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // ---- CTA-pair (cta_group::2) forms -----------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
