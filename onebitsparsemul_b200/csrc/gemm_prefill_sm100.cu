@@ -347,9 +347,11 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   };
-  // Tuning knob for experiments: ONEBIT_PREFILL_VARIANT = <AT><MS><BN/64><NXG> picks a single-CTA
-  // variant; 2 / 22 = CTA-pair kernel with one / two weight tiles per stage; 1 = shape heuristic
-  // without the CTA-pair kernel.
+  // Tuning knob for experiments: ONEBIT_PREFILL_VARIANT = 121 (single CTA, +-1 operand expanded into
+  // shared memory: the first version of this kernel, kept as the baseline of the profiling history),
+  // 1121 / 1141 / 1221 (single CTA, operand in tensor memory: 128 tokens / 256 tokens / two stacked
+  // weight tiles), 2 / 22 (CTA-pair kernel with one / two weight tiles per stage), 1 (shape heuristic
+  // without the CTA-pair kernel).
   static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
   const int64_t row_tiles = m / BM;
   const bool two = (m % 256 == 0);
@@ -379,14 +381,9 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
                 static_cast<const __half*>(scale), d, m, n, k, out_type, status};
   switch (forced) {
     case 121: return launch<1, 128, 1, false>(tmap, a, stream);
-    case 141: return launch<1, 256, 1, false>(tmap, a, stream);
-    case 221: if (two) return launch<2, 128, 1, false>(tmap, a, stream); break;
-    case 222: if (two) return launch<2, 128, 2, false>(tmap, a, stream); break;
     case 1121: return launch<1, 128, 1, true>(tmap, a, stream);
     case 1141: return launch<1, 256, 1, true>(tmap, a, stream);
-    case 1142: return launch<1, 256, 2, true>(tmap, a, stream);
     case 1221: if (two) return launch<2, 128, 1, true>(tmap, a, stream); break;
-    case 1222: if (two) return launch<2, 128, 2, true>(tmap, a, stream); break;
     default: break;
   }
   // Single-CTA variants, all with the +-1 operand in tensor memory: a 256-token tile once it fills

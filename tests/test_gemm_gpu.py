@@ -183,3 +183,50 @@ def test_python_module_forward(lib):
         assert np.allclose(got, want32, rtol=1e-6, atol=1e-6)
         got2 = ob.cuda_binary_mul(layer.packed_binary_sparse, dev(B), layer.meta, scale=layer.scale).cpu().numpy()
         assert (got2 == got).all()
+
+
+# ---- full benchmark sizes: sampled rows against the oracle + size-independent properties ---------------------
+
+def _gpu_weights(m, k, seed):
+    """Random valid 2:4 pattern and signs, generated on the GPU (the benchmark's distributions)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    nib = torch.tensor([0x4, 0x8, 0x9, 0xC, 0xD, 0xE], device="cuda")[torch.randint(0, 6, (m, k // 4), device="cuda", generator=g)]
+    sign = (torch.randint(0, 2, (m, k // 4, 2), device="cuda", generator=g) * 2 - 1).to(torch.float16)
+    w = torch.zeros((m, k // 4, 4), dtype=torch.float16, device="cuda")
+    w.scatter_(2, (nib & 3).unsqueeze(-1), sign[..., 0:1])
+    w.scatter_(2, (nib >> 2).unsqueeze(-1), sign[..., 1:2])
+    scale = torch.empty(m, device="cuda").uniform_(0.01, 0.1, generator=g).to(torch.float16)
+    return w.reshape(m, k), scale
+
+
+@pytest.mark.parametrize("m,n,k", [(8192, 8192, 8192), (28672, 2048, 8192), (8192, 2048, 28672), (25600, 25600, 25600)])
+def test_full_size_sampled_rows_and_linearity(lib, m, n, k):
+    import onebitsparsemul_b200 as ob
+    w, scale = _gpu_weights(m, k, seed=m + k)
+    pw = ob.pack_weight(w, scale=scale, apply_mask=False, keep_reference=False)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(n)
+    B1 = torch.randint(-8, 9, (k, n), device="cuda", generator=g).to(torch.float16)
+    B2 = torch.randint(-8, 9, (k, n), device="cuda", generator=g).to(torch.float16)
+    noscale = ob.PackedWeight(m, k, pw.bits_tile, pw.meta_tile, None)
+    C1 = ob.matmul_packed(noscale, B1)                       # fp32, integer-exact
+    _lib.check(lib.onebit_check_device_status())
+    # (1) 128 sampled rows x 512 sampled columns against the oracle, bit for bit
+    rows = torch.randperm(m, device="cuda", generator=g)[:128].sort().values
+    cols = 512 if n >= 512 else n
+    sub = w[rows].cpu().numpy()
+    canon, signs, _ = oracle.compress(sub)
+    want, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), 0, B1[:, :cols].cpu().numpy(), 128)
+    assert (C1[rows][:, :cols].cpu().numpy() == want).all()
+    # (2) linearity, exact in integers: W(B1 + B2) = W B1 + W B2
+    C2 = ob.matmul_packed(noscale, B2)
+    C12 = ob.matmul_packed(noscale, B1 + B2)
+    assert torch.equal(C12, C1 + C2)
+    del C2, C12
+    # (3) the scaled fp16 output is the rounded scaled fp32 output
+    C16 = ob.matmul_packed(pw, B1, out_dtype=torch.float16)
+    assert torch.equal(C16, (C1 * scale.float()[:, None]).to(torch.float16))
+    # (4) the decode kernel agrees with the tensor-memory kernel on the first 16 tokens
+    Cd = ob.matmul_packed(noscale, B1[:, :16].contiguous(), kernel=_lib.KERNEL_DECODE)
+    assert torch.equal(Cd, C1[:, :16])
