@@ -304,6 +304,68 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_sharded(args):
+    """Supplementary: ONE size^3 GEMM row-sharded over the ranks (strong scaling), optional gather of C."""
+    import torch
+    import torch.distributed as dist
+
+    from onebitsparsemul_b200 import _lib
+    from onebitsparsemul_b200.sharded import ShardedBinaryLinear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    S = args.size
+    layer = ShardedBinaryLinear(S, S)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3080 + rank)
+    rows = layer.rows
+    nib = torch.tensor([0x4, 0x8, 0x9, 0xC, 0xD, 0xE], device=dev)[torch.randint(0, 6, (rows, S // 4), device=dev, generator=g)]
+    sign = (torch.randint(0, 2, (rows, S // 4, 2), device=dev, generator=g) * 2 - 1).to(torch.float16)
+    w = torch.zeros((rows, S // 4, 4), dtype=torch.float16, device=dev)
+    w.scatter_(2, (nib & 3).unsqueeze(-1), sign[..., 0:1])
+    w.scatter_(2, (nib >> 2).unsqueeze(-1), sign[..., 1:2])
+    scale = torch.empty(rows, device=dev).uniform_(0.01, 0.1, generator=g).to(torch.float16)
+    layer.pack_slab(w.reshape(rows, S), scale, apply_mask=False)
+    del w, nib, sign
+    g.manual_seed(3080)                      # B is replicated: same on every rank
+    B = torch.randn((S, S), device=dev, generator=g, dtype=torch.float32).to(torch.float16)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = layer.forward(B, gather=args.gather)
+    _lib.check(lib.onebit_check_device_status())
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = layer.forward(B, gather=args.gather)
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": 2.0 * S * S * S / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+                          "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": f"ONE square GEMM {S}^3 row-sharded over {world} GPU(s), B replicated, "
+                                                 f"gather={args.gather}", "rows_per_rank": layer.rows,
+                                     "out_shape": list(out.shape)}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,9 +374,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--no-decode", action="store_true", help="skip the supplementary decode-regime numbers")
+    ap.add_argument("--workload", default="square", choices=["square", "sharded"],
+                    help="square: one size^3 GEMM per GPU (weak scaling, the contract's line); sharded: ONE size^3 GEMM "
+                         "row-sharded over all ranks (strong scaling, supplementary)")
+    ap.add_argument("--gather", default="none", choices=["none", "all", "overlap"],
+                    help="sharded workload only: gather the full C on every rank")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "sharded":
+        run_sharded(args)
     else:
         run_ours(args)
 

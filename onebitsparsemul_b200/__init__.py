@@ -19,7 +19,7 @@ __all__ = [
     "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
     "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
     "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
-    "relayout", "matmul_rows", "OneBitError",
+    "relayout", "matmul_rows", "replace_linear_layers", "OneBitError",
 ]
 
 
@@ -224,15 +224,17 @@ def matmul_rows(pw: PackedWeight, B, out, row0: int, rows: int, kernel=KERNEL_AU
 # ---- the module (reference: __init__.py:101-145) ----------------------------------------------------------
 
 class BinaryLinear_2_4(nn.Module):
-    """1-bit 2:4 sparse linear layer without bias (reference ``BinaryLinear_2_4``).
+    """1-bit 2:4 sparse linear layer (reference ``BinaryLinear_2_4``, __init__.py:101-145).
 
     Same attributes as the reference (``packed_binary_sparse`` uint8 (in/2, out/8), ``meta`` int16
     (out, in/16), ``vaild``), here registered as buffers together with the tile-ordered operands the
     kernels read, so that ``state_dict`` and ``.to()`` carry them. ``forward(x)`` takes x as the
-    kernel does, (in, tokens), and returns (out, tokens).
+    kernel does, (in, tokens), and returns (out, tokens), like the reference. ``forward_tokens(x)``
+    is the ``nn.Linear`` convention, (..., in) -> (..., out), with the optional bias the reference's
+    model-replace demo attaches (tests/python/test_model_replace.py:40-42).
     """
 
-    def __init__(self, infeatures: int, outfeatures: int, out_dtype=torch.float32):
+    def __init__(self, infeatures: int, outfeatures: int, out_dtype=torch.float32, bias: bool = False):
         super().__init__()
         if infeatures % 128 != 0 or outfeatures % 128 != 0:
             raise ValueError("`infeatures` and `outfeatures` must be divisible by 128.")
@@ -241,20 +243,78 @@ class BinaryLinear_2_4(nn.Module):
         self.register_buffer("meta", torch.zeros((outfeatures, infeatures // 16), dtype=torch.int16))
         self.register_buffer("bits_tile", torch.zeros(outfeatures * infeatures // 16, dtype=torch.uint8))
         self.register_buffer("meta_tile", torch.zeros(outfeatures * infeatures // 8, dtype=torch.uint8))
-        self.register_buffer("scale", None)
-        self.vaild = False
+        self.register_buffer("scale", torch.ones(outfeatures, dtype=torch.float16))
+        self.register_buffer("bias", torch.zeros(outfeatures, dtype=torch.float16) if bias else None)
+        self.register_buffer("packed_flag", torch.zeros((), dtype=torch.uint8))     # makes `vaild` survive state_dict
+        self.vaild = False                # (sic) the reference's attribute name, __init__.py:117
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self.vaild = bool(self.packed_flag.item())
+
+    def _packed(self):
+        # the scale defaults to ones: multiplying by 1 is exact, so an unscaled layer equals the reference's
+        return PackedWeight(self.outfeatures, self.infeatures, self.bits_tile, self.meta_tile, self.scale)
 
     def forward(self, x):
+        """x: (infeatures, tokens) fp16 on the layer's device -> (outfeatures, tokens)."""
         if not self.vaild:
             raise NotImplementedError("the BinaryLinear")
-        pw = PackedWeight(self.outfeatures, self.infeatures, self.bits_tile, self.meta_tile, self.scale)
-        return matmul_packed(pw, x, out_dtype=self.out_dtype)
+        return matmul_packed(self._packed(), x, out_dtype=self.out_dtype)
 
-    def pack(self, weight, scale=None):
+    def forward_tokens(self, x):
+        """x: (..., infeatures) -> (..., outfeatures), the nn.Linear convention (plus bias if present).
+        The kernels take tokens as columns, so the activations are transposed on the way in and out."""
+        if not self.vaild:
+            raise NotImplementedError("the BinaryLinear")
+        lead = x.shape[:-1]
+        xt = x.reshape(-1, self.infeatures).to(torch.float16).t().contiguous()
+        y = matmul_packed(self._packed(), xt, out_dtype=torch.float16).t()
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*lead, self.outfeatures).to(x.dtype if x.dtype.is_floating_point else torch.float16)
+
+    def pack(self, weight, scale=None, bias=None):
         """weight: (outfeatures, infeatures). Mask to 2:4 by magnitude, compress, quantise, pack."""
         if tuple(weight.shape) != (self.outfeatures, self.infeatures):
             raise ValueError(f"weight must be ({self.outfeatures}, {self.infeatures})")
         pw = pack_weight(weight.to(torch.float16) if weight.dtype == torch.float32 else weight, scale=scale)
         self.packed_binary_sparse, self.meta = pw.packed_binary_sparse, pw.meta
-        self.bits_tile, self.meta_tile, self.scale = pw.bits_tile, pw.meta_tile, pw.scale
+        self.bits_tile, self.meta_tile = pw.bits_tile, pw.meta_tile
+        dev = pw.bits_tile.device
+        self.scale = pw.scale if pw.scale is not None else torch.ones(self.outfeatures, dtype=torch.float16, device=dev)
+        if bias is not None:
+            self.bias = bias.detach().to(dev, torch.float16).clone()
+        self.packed_flag = torch.ones((), dtype=torch.uint8, device=dev)
         self.vaild = True
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, out_dtype=torch.float16) -> "BinaryLinear_2_4":
+        """Quantise an ``nn.Linear``: sign bits of the 2:4-masked weight, per-row scale = mean |w| of the
+        kept weights (the scale that minimises the L2 error of a +-scale code), bias carried over."""
+        w = linear.weight.detach()
+        layer = cls(linear.in_features, linear.out_features, out_dtype=out_dtype, bias=linear.bias is not None)
+        wc = w.to("cuda", torch.float16) if not w.is_cuda else w.to(torch.float16)
+        mask = mask_creator(wc)
+        scale = ((wc.float().abs() * mask).sum(1) / mask.sum(1).clamp(min=1)).to(torch.float16)
+        layer = layer.to(wc.device)
+        layer.pack(wc, scale=scale, bias=None if linear.bias is None else linear.bias)
+        return layer
+
+
+def replace_linear_layers(model: nn.Module, skip=("lm_head",), min_features: int = 128) -> int:
+    """Swap every eligible ``nn.Linear`` of `model` for a packed ``BinaryLinear_2_4`` in place (the flow of
+    the reference's tests/python/test_model_replace.py:22-44). A layer is eligible when both feature
+    counts are multiples of 128 and its name is not in `skip`. Returns the number of layers replaced.
+    The replaced layers answer ``module(x)`` with the nn.Linear convention."""
+    replaced = 0
+    for name, child in list(model.named_children()):
+        if isinstance(child, nn.Linear) and name not in skip and child.in_features % 128 == 0 \
+                and child.out_features % 128 == 0 and min(child.in_features, child.out_features) >= min_features:
+            packed = BinaryLinear_2_4.from_linear(child)
+            packed.forward = packed.forward_tokens          # nn.Linear calling convention inside a model
+            setattr(model, name, packed)
+            replaced += 1
+        else:
+            replaced += replace_linear_layers(child, skip, min_features)
+    return replaced

@@ -84,3 +84,54 @@ def test_cli_reference_flags_and_output_lines():
     r = run_cli("--a_rows=4096", "--n=4", "--a_cols=4096", "--out=fp16", "--scale=true", "--reference-check=true", "--json")
     assert r.returncode == 0 and '"passed": true' in r.stdout
     assert "--a_rows" in run_cli("--help").stdout
+
+
+def test_model_replace_flow_and_state_dict_round_trip():
+    """The step above the path (reference: tests/python/test_model_replace.py:22-44) on a synthetic
+    Llama-shaped MLP block: swap nn.Linear layers, run tokens through, save and reload."""
+    import torch.nn as nn
+
+    import onebitsparsemul_b200 as ob
+
+    torch.manual_seed(0)
+
+    class Block(nn.Module):
+        def __init__(self, d=256, f=512):
+            super().__init__()
+            self.gate, self.up, self.down = nn.Linear(d, f, bias=False), nn.Linear(d, f, bias=True), nn.Linear(f, d, bias=False)
+            self.lm_head = nn.Linear(d, 384, bias=False)
+            self.odd = nn.Linear(d, 100)                                   # not a multiple of 128: left alone
+
+        def forward(self, x):
+            return self.down(torch.nn.functional.silu(self.gate(x)) * self.up(x))
+
+    model = Block().cuda().half()
+    x = torch.randn(3, 5, 256, device="cuda", dtype=torch.float16)
+    # what the replaced model should compute: sign(w) * mask * scale in place of w
+    def quantised(lin):
+        w = lin.weight.detach()
+        mask = ob.mask_creator(w)
+        scale = ((w.float().abs() * mask).sum(1) / mask.sum(1)).half()
+        return (torch.sign(w.float()) * mask * scale.float()[:, None]).half()
+    ref = Block().cuda().half()
+    ref.load_state_dict(model.state_dict())
+    for name in ("gate", "up", "down"):
+        getattr(ref, name).weight.data = quantised(getattr(model, name))
+    want = ref(x)
+
+    n = ob.replace_linear_layers(model)
+    assert n == 3 and isinstance(model.gate, ob.BinaryLinear_2_4) and isinstance(model.lm_head, nn.Linear) and isinstance(model.odd, nn.Linear)
+    got = model(x)
+    assert got.shape == want.shape and got.dtype == torch.float16
+    assert torch.allclose(got.float(), want.float(), rtol=2e-2, atol=2e-2 * want.float().abs().max().item())
+
+    # checkpoint / resume: the packed tensors travel in the state dict
+    state = {k: v.cpu() for k, v in model.state_dict().items()}
+    assert {"gate.bits_tile", "gate.meta_tile", "gate.scale", "gate.packed_binary_sparse", "gate.meta", "up.bias"} <= set(state)
+    fresh = Block().half()
+    fresh.gate, fresh.up, fresh.down = ob.BinaryLinear_2_4(256, 512), ob.BinaryLinear_2_4(256, 512, bias=True), ob.BinaryLinear_2_4(512, 256)
+    for m_ in (fresh.gate, fresh.up, fresh.down):
+        m_.forward = m_.forward_tokens
+    fresh.load_state_dict(state)
+    fresh = fresh.cuda()
+    assert fresh.gate.vaild and torch.equal(fresh(x), got)
