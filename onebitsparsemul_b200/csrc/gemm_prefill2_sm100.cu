@@ -103,12 +103,33 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
   const int nit = (kt + KS - 1) / KS;               // pipeline iterations; the last may hold fewer tiles
   long long budget = 2000000000ll;
 
+  // one stage of TMA traffic: own half of the token tile + the weight tiles' metadata and sign blocks
+  auto load_stage = [&](int it) {
+    const int s = it % C::kStages;
+    const int tiles = min(KS, kt - it * KS);
+    // token rows past k (odd tile count) are zero-filled by TMA and still count as bytes
+    mbar_expect_tx(bar_full(s), C::kBBytes + tiles * (OB_TILE_META_BYTES + OB_TILE_BITS_BYTES));
+#pragma unroll
+    for (int j = 0; j < BNH / 64; ++j)
+      tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * KS * BK, bar_full(s));
+    for (int j = 0; j < tiles; ++j) {
+      const int64_t tile = mt * kt + it * KS + j;
+      bulk_load(stage_e(s, j), a.meta_tile + tile * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
+      bulk_load(stage_bits(s, j), a.bits_tile + tile * OB_TILE_BITS_BYTES, OB_TILE_BITS_BYTES, bar_full(s));
+    }
+  };
+  const int npre = min(C::kStages, nit);            // stages filled before anything else happens
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
     for (int x = 0; x < C::kASlots; ++x) mbar_init(bar_afull(x), 2 * 4 * NXG);
     mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+    if (a.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_c) : "memory");
+    // the first ring of loads only needs this CTA's own barriers: start it now, so that its latency
+    // overlaps the tensor-memory allocation and the cluster-wide start-up barrier
+    for (int it = 0; it < npre; ++it) load_stage(it);
   }
   if (threadIdx.x == 0) OB_TRACE_EV(7, 2);
   if (warp == 1) tcgen05_alloc_2cta(tmem_slot, C::kTmemCols);
@@ -123,23 +144,12 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
   const uint32_t tmem_a = tmem_base + C::kAccCols + C::kECols;
 
   if (warp == 0) {
-    // ---------------- producer (both CTAs) ----------------
+    // ---------------- producer (both CTAs): the stages after the pre-issued first ring ----------------
     if (lane == 0) {
-      for (int it = 0; it < nit; ++it) {
-        const int s = it % C::kStages;
-        const int tiles = min(KS, kt - it * KS);
-        mbar_wait(bar_empty(s), ((it / C::kStages) & 1) ^ 1, budget, a.status, 1);
+      for (int it = npre; it < nit; ++it) {
+        mbar_wait(bar_empty(it % C::kStages), ((it / C::kStages) & 1) ^ 1, budget, a.status, 1);
         OB_TRACE_EV(0, it);
-        // token rows past k (odd tile count) are zero-filled by TMA and still count as bytes
-        mbar_expect_tx(bar_full(s), C::kBBytes + tiles * (OB_TILE_META_BYTES + OB_TILE_BITS_BYTES));
-#pragma unroll
-        for (int j = 0; j < BNH / 64; ++j)
-          tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * KS * BK, bar_full(s));
-        for (int j = 0; j < tiles; ++j) {
-          const int64_t tile = mt * kt + it * KS + j;
-          bulk_load(stage_e(s, j), a.meta_tile + tile * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
-          bulk_load(stage_bits(s, j), a.bits_tile + tile * OB_TILE_BITS_BYTES, OB_TILE_BITS_BYTES, bar_full(s));
-        }
+        load_stage(it);
       }
     }
   } else if (warp == 1) {
