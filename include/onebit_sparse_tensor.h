@@ -85,6 +85,20 @@ int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, in
 int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
+/* The same GEMM for tokens and results that live in (pinned) HOST memory: b_host fp16 (k, n) and d_host
+ * (m, n), both row-major. The reference's Python wrapper hands the kernel a CPU-allocated C
+ * (onebit_sparse_mul/__init__.py:12-15); here the transfers are part of the call and overlap the
+ * compute: token column panels go host -> device, are multiplied and return device -> host in a
+ * three-slot pipeline on internal streams, so a call costs about max(H2D, D2H). `workspace` is DEVICE
+ * memory of onebit_host_workspace_bytes(m, n, k, out_type) bytes, 256-byte aligned, owned by the caller
+ * and busy until the work queued by this call has finished. Asynchronous like the other calls: work
+ * queued on `stream` before the call precedes it, work queued after it follows it. Concurrent calls on
+ * one device share the internal streams and therefore serialise. Needs n % 8 == 0. */
+size_t onebit_host_workspace_bytes(int64_t m, int64_t n, int64_t k, int out_type);
+int onebit_matmul_packed_host(const void *bits_tile, const void *meta_tile, const void *scale, const void *b_host,
+                              void *d_host, int64_t m, int64_t n, int64_t k, int out_type, void *workspace,
+                              size_t workspace_bytes, void *stream);
+
 /* Dense (m, k) row-major weights -> packed operands in one pass; bit-exact replacement of
  * sparse_semi_structured_from_dense_cutlass + binary_quant + .T + pack_binary
  * (_semi_structured_conversions.py:54-179, onebit_sparse_mul/__init__.py:22-34,139-143).

@@ -19,7 +19,7 @@ __all__ = [
     "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
     "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
     "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
-    "relayout", "matmul_rows", "replace_linear_layers", "OneBitError",
+    "relayout", "matmul_rows", "matmul_packed_host", "replace_linear_layers", "OneBitError",
 ]
 
 
@@ -199,6 +199,36 @@ def matmul_packed(pw: PackedWeight, B, out=None, out_dtype=torch.float32, kernel
         _lib.check(lib.onebit_matmul_packed(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(B), _ptr(out),
                                             pw.m, n, pw.k, _out_code(out.dtype), kernel, _stream()))
     return out
+
+
+_host_ws = {}
+
+
+def matmul_packed_host(pw: PackedWeight, B_host, out_host=None, out_dtype=torch.float16):
+    """C = pw @ B for tokens B (k, n) in pinned HOST memory, result into pinned host memory: column
+    panels of B travel to the GPU, are multiplied and travel back in an overlapped three-stage pipeline
+    (``onebit_matmul_packed_host``). Returns the host tensor; the work is queued asynchronously on the
+    current stream of the weight's device, so synchronise that stream before reading the result."""
+    lib = _lib.load()
+    if B_host.is_cuda or B_host.dtype != torch.float16 or B_host.shape[0] != pw.k or not B_host.is_contiguous():
+        raise ValueError("B_host must be a contiguous CPU float16 tensor of shape (k, n)")
+    if not B_host.is_pinned():
+        raise ValueError("B_host must be pinned (page-locked) host memory")
+    n = B_host.shape[1]
+    if out_host is None:
+        out_host = torch.empty((pw.m, n), dtype=out_dtype).pin_memory()
+    if out_host.is_cuda or not out_host.is_pinned() or tuple(out_host.shape) != (pw.m, n) or not out_host.is_contiguous():
+        raise ValueError("out_host must be a contiguous pinned CPU tensor of shape (m, n)")
+    dev = pw.bits_tile.device
+    code = _out_code(out_host.dtype)
+    need = lib.onebit_host_workspace_bytes(pw.m, n, pw.k, code)
+    ws = _host_ws.get(dev)
+    if ws is None or ws.numel() < need:
+        ws = _host_ws[dev] = torch.empty(need, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.onebit_matmul_packed_host(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), B_host.data_ptr(),
+                                                 out_host.data_ptr(), pw.m, n, pw.k, code, _ptr(ws), ws.numel(), _stream()))
+    return out_host
 
 
 def matmul_rows(pw: PackedWeight, B, out, row0: int, rows: int, kernel=KERNEL_AUTO):

@@ -135,3 +135,24 @@ def test_model_replace_flow_and_state_dict_round_trip():
     fresh.load_state_dict(state)
     fresh = fresh.cuda()
     assert fresh.gate.vaild and torch.equal(fresh(x), got)
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 64, 256), (512, 4096, 1024), (1024, 2056, 512)])
+def test_host_buffer_entry_point_equals_device_path(m, n, k):
+    """onebit_matmul_packed_host (pinned host tokens in, pinned host result out, pipelined copies) gives
+    the bits the device-resident call gives, also when the last column panel is ragged (integer tokens:
+    a narrow last panel may run on another kernel, whose summation order differs)."""
+    import onebitsparsemul_b200 as ob
+    rng = np.random.default_rng(m + n)
+    dense, scale = helpers.make_weights(rng, m, k)
+    pw = ob.pack_weight(torch.from_numpy(dense), scale=torch.from_numpy(scale), apply_mask=False)
+    Bh = torch.from_numpy(helpers.make_tokens(rng, k, n, "int")).pin_memory()
+    for dtype in (torch.float16, torch.float32):
+        want = ob.matmul_packed(pw, Bh.cuda(), out_dtype=dtype)
+        for _ in range(2):                                   # twice: slot reuse across calls
+            Ch = torch.full((m, n), float("nan"), dtype=dtype).pin_memory()
+            ob.matmul_packed_host(pw, Bh, Ch)
+            torch.cuda.synchronize()
+            assert torch.equal(Ch, want.cpu())
+    with pytest.raises(ValueError):
+        ob.matmul_packed_host(pw, torch.zeros((k, n), dtype=torch.float16))     # not pinned
