@@ -85,6 +85,18 @@ int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, in
 int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
+/* The same product in the nn.Linear convention, for callers that keep activations token-major:
+ *   y (n, m) = x (n, k) @ W^T (+ bias),  x fp16 row-major, y fp16 / fp32 row-major, bias fp16 (m) or NULL,
+ * W given by its tile-ordered operands and optional per-row scale. It is C^T = (A_sparse x B)^T with
+ * B = x^T, computed without any transposition pass: x is loaded as a K-major tensor-core operand and
+ * the epilogue writes the transposed tile. This is what the reference's model-replace demo needs
+ * (tests/python/test_model_replace.py:22-44; its forward passes x straight through,
+ * onebit_sparse_mul/__init__.py:118-128). n <= 16 runs on the split-K cluster kernel, more tokens on
+ * the CTA-pair tensor-memory kernel (needs m % 256 == 0; otherwise the cluster kernel serves any n).
+ * x must be 16-byte aligned. kernel: ONEBIT_KERNEL_*. */
+int onebit_linear_tokens(const void *bits_tile, const void *meta_tile, const void *scale, const void *bias, const void *x,
+                         void *y, int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
+
 /* The same GEMM for tokens and results that live in (pinned) HOST memory: b_host fp16 (k, n) and d_host
  * (m, n), both row-major. The reference's Python wrapper hands the kernel a CPU-allocated C
  * (onebit_sparse_mul/__init__.py:12-15); here the transfers are part of the call and overlap the

@@ -19,7 +19,7 @@ __all__ = [
     "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
     "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
     "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
-    "relayout", "matmul_rows", "matmul_packed_host", "replace_linear_layers", "OneBitError",
+    "relayout", "matmul_rows", "matmul_packed_host", "linear_tokens", "replace_linear_layers", "OneBitError",
 ]
 
 
@@ -201,6 +201,23 @@ def matmul_packed(pw: PackedWeight, B, out=None, out_dtype=torch.float32, kernel
     return out
 
 
+def linear_tokens(pw: PackedWeight, x, bias=None, out_dtype=torch.float16, kernel=KERNEL_AUTO):
+    """y (..., m) = x (..., k) @ W^T (+ bias): the nn.Linear convention, no transposition pass
+    (``onebit_linear_tokens``). x: CUDA float16, last dimension k."""
+    lib = _lib.load()
+    if not x.is_cuda or x.dtype != torch.float16 or x.shape[-1] != pw.k:
+        raise ValueError("x must be a CUDA float16 tensor whose last dimension is k")
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, pw.k).contiguous()
+    n = x2.shape[0]
+    y = torch.empty((n, pw.m), dtype=out_dtype, device=x.device)
+    if n > 0:
+        with torch.cuda.device(x.device):
+            _lib.check(lib.onebit_linear_tokens(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(bias), _ptr(x2),
+                                                _ptr(y), pw.m, n, pw.k, _out_code(out_dtype), kernel, _stream()))
+    return y.reshape(*lead, pw.m)
+
+
 _host_ws = {}
 
 
@@ -294,15 +311,11 @@ class BinaryLinear_2_4(nn.Module):
 
     def forward_tokens(self, x):
         """x: (..., infeatures) -> (..., outfeatures), the nn.Linear convention (plus bias if present).
-        The kernels take tokens as columns, so the activations are transposed on the way in and out."""
+        Token-major kernels: x is read as it lies and y is written as it lies, nothing is transposed."""
         if not self.vaild:
             raise NotImplementedError("the BinaryLinear")
-        lead = x.shape[:-1]
-        xt = x.reshape(-1, self.infeatures).to(torch.float16).t().contiguous()
-        y = matmul_packed(self._packed(), xt, out_dtype=torch.float16).t()
-        if self.bias is not None:
-            y = y + self.bias
-        return y.reshape(*lead, self.outfeatures).to(x.dtype if x.dtype.is_floating_point else torch.float16)
+        y = linear_tokens(self._packed(), x.to(torch.float16), bias=self.bias, out_dtype=torch.float16)
+        return y if x.dtype == torch.float16 or not x.dtype.is_floating_point else y.to(x.dtype)
 
     def pack(self, weight, scale=None, bias=None):
         """weight: (outfeatures, infeatures). Mask to 2:4 by magnitude, compress, quantise, pack."""

@@ -157,6 +157,34 @@ int onebit_matmul_packed(const void* bits_tile, const void* meta_tile, const voi
   return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, static_cast<cudaStream_t>(stream));
 }
 
+int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias, const void* x,
+                         void* y, int64_t m, int64_t n, int64_t k, int out_type, int kernel, void* stream) {
+  if (!bits_tile || !meta_tile || !x || !y) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (!tiled_shape(m, k) || n < 1)
+    return fail(ONEBIT_ERR_SHAPE, "token-major GEMM needs m %% 128 == 0, k %% 128 == 0, n >= 1 (got m=%lld n=%lld k=%lld)",
+                (long long)m, (long long)n, (long long)k);
+  if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type %d", out_type);
+  if (reinterpret_cast<uintptr_t>(x) & 15) return fail(ONEBIT_ERR_ARG, "x must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kernel == ONEBIT_KERNEL_AUTO)
+    kernel = (n > 16 && ob::prefill_tokens_supported(m, n, k)) ? ONEBIT_KERNEL_PREFILL : ONEBIT_KERNEL_DECODE;
+  cudaError_t e;
+  if (kernel == ONEBIT_KERNEL_PREFILL) {
+    if (!ob::prefill_tokens_supported(m, n, k))
+      return fail(ONEBIT_ERR_SHAPE, "the token-major tensor-memory kernel needs m %% 256 == 0 (got m=%lld)", (long long)m);
+    int* status = nullptr;
+    if (int rc = get_status_word(&status)) return rc;
+    e = ob::launch_gemm_prefill_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, status, st);
+    if (e != cudaSuccess) return cuda_fail(e, "token-major tensor-memory GEMM launch");
+  } else if (kernel == ONEBIT_KERNEL_DECODE) {
+    e = ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, st);
+    if (e != cudaSuccess) return cuda_fail(e, "token-major decode GEMM launch");
+  } else {
+    return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
+  }
+  return ONEBIT_OK;
+}
+
 int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const void* e_meta, const void* scale, int64_t m,
                             int64_t n, int64_t k, int out_type, int meta_dialect, void* workspace, size_t workspace_bytes,
                             void* stream) {

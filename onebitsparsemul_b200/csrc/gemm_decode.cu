@@ -76,13 +76,15 @@ struct DecodeArgs {
   const uint8_t* bits_tile;
   const uint8_t* meta_tile;
   const __half* scale;
+  const __half* bias;   // per output row, added after the scale (token-major callers; NULL = none)
   const __half* b;
   void* d;
   int64_t m, n, k;
 };
 
 // NT = number of 8-token tiles per pass (1 or 2)
-template <int NT, typename OutT>
+// TM = token-major operands (the nn.Linear convention): b is x (n, k) row-major, d is y (n, m) row-major
+template <int NT, typename OutT, bool TM>
 __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
   constexpr int NP = NT * 8;
   __shared__ __align__(16) __half s_b[2][NP * kBtStride];          // per half: s_b[j][kk] = B[k0 + kk][n0 + j]
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
       for (int i = 0; i < 4; ++i) acc[c][nt][i] = 0.f;
 
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
-  const bool vec_rows = (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
+  const bool vec_rows = !TM && (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
   __half* sb = s_b[half];
 
   for (int64_t chunk = tile_begin; chunk < tile_end; chunk += kChunkTiles) {
@@ -147,7 +149,16 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
     // 2. tokens of the chunk: sb[kk][j] = B[k0 + kk][n0 + j], zero beyond n
     const int64_t k0 = chunk * OB_TILE_K;
     const int kc = ntile * OB_TILE_K;
-    if (vec_rows) {
+    if constexpr (TM) {
+      // token j is a contiguous row of x: 16-byte pieces along k, zero rows beyond n
+      const int pieces = kc / 8;
+      for (int idx = tid_h; idx < NP * pieces; idx += 256) {
+        const int j = idx / pieces, pc = idx - j * pieces;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (j < nvalid) v = __ldg(reinterpret_cast<const uint4*>(a.b + (n0 + j) * a.k + k0 + pc * 8));
+        *reinterpret_cast<uint4*>(&sb[j * kBtStride + pc * 8]) = v;
+      }
+    } else if (vec_rows) {
       constexpr int kPieces = NP / 8;                         // 16-byte pieces per token row
       for (int idx = tid_h; idx < kc * kPieces; idx += 256) {
         const int kk = idx / kPieces, pc = idx % kPieces;
@@ -213,20 +224,23 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
 
   // 5. fixed-order sum of the 2S slices from this CTA's own shared memory
   for (int e = threadIdx.x; e < rows_per * NP; e += 512) {
-    const int rr = e / NP, j = e % NP;
+    // consecutive threads walk the fastest output dimension: tokens of a row (m x n), rows of a token (n x m)
+    const int rr = TM ? e % rows_per : e / NP, j = TM ? e / rows_per : e % NP;
     float sum = 0.f;
     for (int sl = 0; sl < slices; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
     const int64_t row = mb * 128 + rank * rows_per + rr;
     if (a.scale) sum *= __half2float(a.scale[row]);
+    if (a.bias) sum += __half2float(a.bias[row]);
     if (j < nvalid) {
-      if constexpr (sizeof(OutT) == 2) static_cast<__half*>(a.d)[row * a.n + n0 + j] = __float2half_rn(sum);
-      else static_cast<float*>(a.d)[row * a.n + n0 + j] = sum;
+      const int64_t o = TM ? (n0 + j) * a.m + row : row * a.n + n0 + j;
+      if constexpr (sizeof(OutT) == 2) static_cast<__half*>(a.d)[o] = __float2half_rn(sum);
+      else static_cast<float*>(a.d)[o] = sum;
     }
   }
   OB_TRACE_EV(7);
 }
 
-template <int NT, typename OutT>
+template <int NT, typename OutT, bool TM>
 cudaError_t launch(const DecodeArgs& a, int S, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(a.m / 128), (unsigned)S, (unsigned)((a.n + NT * 8 - 1) / (NT * 8)));
@@ -240,17 +254,15 @@ cudaError_t launch(const DecodeArgs& a, int S, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, ob_gemm_decode_kernel<NT, OutT>, a);
+  return cudaLaunchKernelEx(&cfg, ob_gemm_decode_kernel<NT, OutT, TM>, a);
 }
 
 }  // namespace
 
 namespace ob {
 
-cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
-                               void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream) {
-  DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-               static_cast<const __half*>(scale), static_cast<const __half*>(b), d, m, n, k};
+namespace {
+int pick_split(int64_t m, int64_t k) {
   // split K over a cluster of up to 8 CTAs (16 slices), as far as there are tiles and until the
   // grid holds about two CTAs per SM
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
@@ -259,9 +271,30 @@ cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, con
   // tuning knob for experiments
   static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_SPLIT"); return v ? atoi(v) : 0; }();
   if (forced == 1 || forced == 2 || forced == 4 || forced == 8) S = forced;
-  const bool two = (n > 8);
-  if (out_type == OB_OUT_F16) return two ? launch<2, __half>(a, S, stream) : launch<1, __half>(a, S, stream);
-  return two ? launch<2, float>(a, S, stream) : launch<1, float>(a, S, stream);
+  return S;
+}
+template <bool TM>
+cudaError_t dispatch(const DecodeArgs& a, int out_type, cudaStream_t stream) {
+  const int S = pick_split(a.m, a.k);
+  const bool two = (a.n > 8);
+  if (out_type == OB_OUT_F16) return two ? launch<2, __half, TM>(a, S, stream) : launch<1, __half, TM>(a, S, stream);
+  return two ? launch<2, float, TM>(a, S, stream) : launch<1, float, TM>(a, S, stream);
+}
+}  // namespace
+
+cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                               void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream) {
+  DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
+               static_cast<const __half*>(scale), nullptr, static_cast<const __half*>(b), d, m, n, k};
+  return dispatch<false>(a, out_type, stream);
+}
+
+cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                      const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
+                                      cudaStream_t stream) {
+  DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
+               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(x), y, m, n, k};
+  return dispatch<true>(a, out_type, stream);
 }
 
 }  // namespace ob

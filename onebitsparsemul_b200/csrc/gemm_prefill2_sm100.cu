@@ -67,6 +67,7 @@ struct Prefill2Args {
   const uint8_t* bits_tile;
   const uint8_t* meta_tile;
   const __half* scale;
+  const __half* bias;  // per output row, added after the scale (token-major callers; NULL = none)
   void* d;
   int64_t m, n, k;
   int out_type;
@@ -74,7 +75,9 @@ struct Prefill2Args {
   int tma_store;     // 1: fp16 output leaves through shared memory and TMA stores (tmap_c is valid)
 };
 
-template <int KS>
+// TM = token-major operands, the nn.Linear convention: tokens x (n, k) row-major, i.e. a K-major B operand,
+//      and output y (n, m) row-major, i.e. C transposed. false = the reference's B (k, n), C (m, n).
+template <int KS, bool TM>
 __global__ void __launch_bounds__(Cfg2<KS>::kThreads, 1)
 ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c,
                         Prefill2Args a) {
@@ -109,9 +112,16 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
     const int tiles = min(KS, kt - it * KS);
     // token rows past k (odd tile count) are zero-filled by TMA and still count as bytes
     mbar_expect_tx(bar_full(s), C::kBBytes + tiles * (OB_TILE_META_BYTES + OB_TILE_BITS_BYTES));
+    if constexpr (TM) {
+      // K-major token tile: boxes of 64 k (128 bytes) x 128 tokens, two per weight tile
 #pragma unroll
-    for (int j = 0; j < BNH / 64; ++j)
-      tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * KS * BK, bar_full(s));
+      for (int j = 0; j < 2 * KS; ++j)
+        tma_load_2d(stage_b(s) + j * (BNH * 128), &tmap_b, (it * KS * BK) + 64 * j, (int)n0, bar_full(s));
+    } else {
+#pragma unroll
+      for (int j = 0; j < BNH / 64; ++j)
+        tma_load_2d(stage_b(s) + j * C::kBBoxBytes, &tmap_b, (int)(n0 + 64 * j), it * KS * BK, bar_full(s));
+    }
     for (int j = 0; j < tiles; ++j) {
       const int64_t tile = mt * kt + it * KS + j;
       bulk_load(stage_e(s, j), a.meta_tile + tile * OB_TILE_META_BYTES, OB_TILE_META_BYTES, bar_full(s));
@@ -155,7 +165,7 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (cta == 0 && lane == 0) {
-      const uint32_t idesc = (1u << 2) /*sparse*/ | (1u << 4) /*fp32 accumulate*/ | (1u << 16) /*B is n-major*/ |
+      const uint32_t idesc = (1u << 2) /*sparse*/ | (1u << 4) /*fp32 accumulate*/ | (TM ? 0u : (1u << 16)) /*B n-major*/ |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
       for (int it = 0; it < nit; ++it) {
         const int s = it % C::kStages, x = s;
@@ -170,10 +180,14 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
             const uint32_t e_col = tmem_e + 8 * j + 4 * (it & 1);
             tcgen05_cp_128x128b_2cta(e_col, make_desc(stage_e(s, j), 128, 128, kLayoutNone));
 #pragma unroll
-            for (int kb = 0; kb < 4; ++kb)
-              tcgen05_mma_sp_f16_ts_2cta(tmem_acc, tmem_a + x * C::kASlotCols + 32 * j + 8 * kb,
-                                         bdesc + (uint64_t)(1024 * j + 256 * kb), e_col + (kb & ~1),
+            for (int kb = 0; kb < 4; ++kb) {
+              // token tile of k-block kb of weight tile j: 32 k-rows (4 KiB) further in the n-major form;
+              // in the K-major form box 2j + kb/2 (16 KiB each), 64 bytes along its swizzled rows for odd kb
+              const uint64_t bd = TM ? make_desc(stage_b(s) + (2 * j + (kb >> 1)) * (BNH * 128) + (kb & 1) * 64, 16, 1024, kLayoutSw128)
+                                     : bdesc + (uint64_t)(1024 * j + 256 * kb);
+              tcgen05_mma_sp_f16_ts_2cta(tmem_acc, tmem_a + x * C::kASlotCols + 32 * j + 8 * kb, bd, e_col + (kb & ~1),
                                          idesc | (uint32_t)(kb & 1), (it | j | kb) != 0);
+            }
           }
         }
         tcgen05_commit_2cta(bar_empty(s), 3);     // frees stage s and operand slot s in both CTAs
@@ -218,6 +232,53 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
     const int64_t row = mt * BM + q * 32 + lane;
     const int64_t nbase = (int64_t)blockIdx.y * BN;
     const float sc = a.scale ? __half2float(a.scale[row]) : 1.f;
+    const bool has_bias = a.bias != nullptr;
+    const float bs = has_bias ? __half2float(a.bias[row]) : 0.f;
+    auto fin = [&](uint32_t acc) { const float x = __uint_as_float(acc) * sc; return has_bias ? x + bs : x; };
+    if constexpr (TM) {
+      // y (n, m) row-major: this thread owns output feature `row`; the 32 accumulator columns of a chunk
+      // are 32 tokens, i.e. 32 rows of y
+      if (a.tma_store) {
+        // fp16: the transposed tile is assembled in the idle first pipeline stage as 2 boxes of
+        // 256 tokens x 64 features (128-byte swizzle) and leaves with 2 TMA stores
+        uint8_t* cbuf = smem_gen + (stage_b(0) - smem_base);
+        const int r = q * 32 + lane;
+        uint8_t* mybox = cbuf + (r >> 6) * (BN * 128) + (r & 7) * 2;
+        const int chunk = (r & 63) >> 3;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = c0 + j;
+            *reinterpret_cast<__half*>(mybox + t * 128 + ((chunk ^ (t & 7)) << 4)) = __float2half_rn(fin(v[j]));
+          }
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
+        if (q == 0 && lane == 0) {
+#pragma unroll
+          for (int bx = 0; bx < 2; ++bx)
+            tma_store_2d(&tmap_c, smem_u32(cbuf) + bx * (BN * 128), (int)(mt * BM + 64 * bx), (int)nbase);
+          tma_store_commit_and_wait();
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int64_t t = nbase + c0 + j;
+            if (t < a.n) {
+              if (a.out_type == OB_OUT_F16) static_cast<__half*>(a.d)[t * a.m + row] = __float2half_rn(fin(v[j]));
+              else static_cast<float*>(a.d)[t * a.m + row] = fin(v[j]);
+            }
+          }
+        }
+      }
+    } else
     if (a.tma_store) {
       // fp16 output: the tile is assembled in the (now idle) first pipeline stage as 4 boxes of
       // 128 rows x 64 tokens with the 128-byte swizzle, then written with 4 TMA stores: full-line
@@ -235,7 +296,7 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
           uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
+            const __half2 p = __floats2half2_rn(fin(v[8 * j + 2 * h]), fin(v[8 * j + 2 * h + 1]));
             ow[h] = *reinterpret_cast<const uint32_t*>(&p);
           }
           const int chunk = ((c0 & 63) >> 3) + j;              // 16-byte chunk inside the 128-byte box row
@@ -266,7 +327,7 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
             uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int h = 0; h < 4; ++h) {
-              const __half2 p = __floats2half2_rn(__uint_as_float(v[8 * j + 2 * h]) * sc, __uint_as_float(v[8 * j + 2 * h + 1]) * sc);
+              const __half2 p = __floats2half2_rn(fin(v[8 * j + 2 * h]), fin(v[8 * j + 2 * h + 1]));
               ow[h] = *reinterpret_cast<const uint32_t*>(&p);
             }
             *reinterpret_cast<uint4*>(dst + 8 * j) = o;
@@ -277,8 +338,7 @@ ob_gemm_prefill2_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (col + 4 * j < a.n) {
-            float4 o = make_float4(__uint_as_float(v[4 * j]) * sc, __uint_as_float(v[4 * j + 1]) * sc,
-                                   __uint_as_float(v[4 * j + 2]) * sc, __uint_as_float(v[4 * j + 3]) * sc);
+            float4 o = make_float4(fin(v[4 * j]), fin(v[4 * j + 1]), fin(v[4 * j + 2]), fin(v[4 * j + 3]));
             *reinterpret_cast<float4*>(dst + 4 * j) = o;
           }
         }
@@ -306,14 +366,14 @@ bool prefill2_supported(int64_t m, int64_t n, int64_t k) {
 }
 
 namespace {
-template <int KS>
+template <int KS, bool TM>
 cudaError_t launch2(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const Prefill2Args& a, cudaStream_t stream) {
   using C = Cfg2<KS>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill2_kernel<KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill2_kernel<KS, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -329,20 +389,25 @@ cudaError_t launch2(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const Pr
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill2_kernel<KS>, tmap, tmap_c, a);
+  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill2_kernel<KS, TM>, tmap, tmap_c, a);
 }
 }  // namespace
 
-// tmap: tensor map of B with a box of 64 tokens x (128 * ks) k-rows, 128-byte swizzle
-// tmap_c: tensor map of an fp16 C (m x n row-major) with boxes of 64 tokens x 128 rows, 128-byte swizzle,
-//         or NULL (fp32 output, or C not 16-byte aligned): direct stores from registers
-cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, const void* bits_tile,
-                                 const void* meta_tile, const void* scale, void* d, int64_t m, int64_t n, int64_t k,
-                                 int out_type, int* status, cudaStream_t stream) {
+// tmap:   tensor map of the tokens -- reference form: B (k x n), boxes of 64 tokens x (128 * ks) k-rows;
+//         token-major form: x (n x k), boxes of 64 k x 128 tokens; 128-byte swizzle either way
+// tmap_c: tensor map of an fp16 output with the 128-byte swizzle -- C (m x n): boxes of 64 tokens x 128 rows;
+//         y (n x m): boxes of 64 features x 256 tokens -- or NULL (fp32 output, or an output that is not
+//         16-byte aligned): direct stores from registers
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, bool token_major,
+                                 const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                 void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                 cudaStream_t stream) {
   Prefill2Args a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-                 static_cast<const __half*>(scale), d, m, n, k, out_type, status, tmap_c != nullptr};
+                 static_cast<const __half*>(scale), static_cast<const __half*>(bias), d, m, n, k, out_type, status,
+                 tmap_c != nullptr};
   const CUtensorMap& tc = tmap_c ? *tmap_c : *tmap;          // unused when tma_store == 0
-  return ks == 2 ? launch2<2>(*tmap, tc, a, stream) : launch2<1>(*tmap, tc, a, stream);
+  if (token_major) return ks == 2 ? launch2<2, true>(*tmap, tc, a, stream) : launch2<1, true>(*tmap, tc, a, stream);
+  return ks == 2 ? launch2<2, false>(*tmap, tc, a, stream) : launch2<1, false>(*tmap, tc, a, stream);
 }
 
 }  // namespace ob

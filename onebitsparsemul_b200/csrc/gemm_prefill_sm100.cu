@@ -323,9 +323,10 @@ cudaError_t launch(const CUtensorMap& tmap, const PrefillArgs& a, cudaStream_t s
 namespace ob {
 
 bool prefill2_supported(int64_t m, int64_t n, int64_t k);
-cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, const void* bits_tile,
-                                 const void* meta_tile, const void* scale, void* d, int64_t m, int64_t n, int64_t k,
-                                 int out_type, int* status, cudaStream_t stream);
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, bool token_major,
+                                 const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                 void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                 cudaStream_t stream);
 
 bool prefill_supported(int64_t m, int64_t n, int64_t k) {
   return m % BM == 0 && k % BK == 0 && n % 8 == 0 && n >= 8 && k >= BK;
@@ -372,8 +373,8 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
       c_map = encode(&tmap_c, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
     }
-    return launch_gemm_prefill2(&tmap2, c_map ? &tmap_c : nullptr, ks, bits_tile, meta_tile, scale, d, m, n, k, out_type,
-                                status, stream);
+    return launch_gemm_prefill2(&tmap2, c_map ? &tmap_c : nullptr, ks, false, bits_tile, meta_tile, scale, nullptr, d, m, n,
+                                k, out_type, status, stream);
   }
   CUtensorMap tmap;
   if (!make_map(&tmap, BK)) return cudaErrorInvalidValue;
@@ -392,6 +393,40 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   if (n > 128 && row_tiles * ((n + 255) / 256) >= 148) return launch<1, 256, 1, true>(tmap, a, stream);
   if (two && (row_tiles / 2) * ((n + 127) / 128) >= 148) return launch<2, 128, 1, true>(tmap, a, stream);
   return launch<1, 128, 1, true>(tmap, a, stream);
+}
+
+bool prefill_tokens_supported(int64_t m, int64_t n, int64_t k) { return prefill2_supported(m, 8, k) && n >= 1; }
+
+// Token-major form (the nn.Linear convention): x (n, k) row-major fp16, y (n, m) row-major, optional
+// bias (m). Always the CTA-pair kernel: the token tile is a K-major operand loaded straight from x,
+// the epilogue writes the transposed tile, so no transposition pass exists anywhere.
+cudaError_t launch_gemm_prefill_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                       cudaStream_t stream) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return cudaErrorMisalignedAddress;
+  CUtensorMap tmap_x, tmap_y;
+  const cuuint32_t estr[2] = {1, 1};
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)n};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    const cuuint32_t box[2] = {64, 128};
+    if (encode(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  bool y_map = false;
+  if (out_type == OB_OUT_F16 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    const cuuint64_t dims[2] = {(cuuint64_t)m, (cuuint64_t)n};
+    const cuuint64_t strides[1] = {(cuuint64_t)m * 2};
+    const cuuint32_t box[2] = {64, 256};
+    y_map = encode(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, y, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  return launch_gemm_prefill2(&tmap_x, y_map ? &tmap_y : nullptr, 2, true, bits_tile, meta_tile, scale, bias, y, m, n, k,
+                              out_type, status, stream);
 }
 
 }  // namespace ob

@@ -30,5 +30,13 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
                                 void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
                                 cudaStream_t stream);
 bool prefill_supported(int64_t m, int64_t n, int64_t k);
+// token-major forms (x (n, k), y (n, m), optional bias (m)): the nn.Linear convention
+cudaError_t launch_gemm_prefill_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                       cudaStream_t stream);
+bool prefill_tokens_supported(int64_t m, int64_t n, int64_t k);
+cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                      const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
+                                      cudaStream_t stream);
 
 }  // namespace ob

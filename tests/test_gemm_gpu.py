@@ -230,3 +230,43 @@ def test_full_size_sampled_rows_and_linearity(lib, m, n, k):
     # (4) the decode kernel agrees with the tensor-memory kernel on the first 16 tokens
     Cd = ob.matmul_packed(noscale, B1[:, :16].contiguous(), kernel=_lib.KERNEL_DECODE)
     assert torch.equal(Cd, C1[:, :16])
+
+
+# ---- token-major form (nn.Linear convention): y (n, m) = x (n, k) @ W^T + bias ---------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(256, 1, 256), (256, 5, 384), (512, 16, 1024), (256, 17, 256), (512, 200, 640),
+                                   (1024, 256, 512), (2048, 1000, 1024), (384, 40, 256), (4096, 2048, 4096)])
+def test_token_major_entry_point(lib, m, n, k):
+    p = Problem(3 * m + n + k, m, k)
+    rng = p.rng
+    bias = rng.integers(-4, 5, size=m).astype(np.float16)
+    # exact: integer tokens and bias, no scale, fp32 out
+    x = helpers.make_tokens(rng, n, k, "int")                     # (n, k): token-major
+    want32, _ = p.oracle(np.ascontiguousarray(x.T), use_scale=False)
+    want = want32.T + bias.astype(np.float32)[None, :]
+    d_x, d_bias = dev(x), dev(bias)
+    y = torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(lib.onebit_linear_tokens(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), None, d_bias.data_ptr(),
+                                        d_x.data_ptr(), y.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_AUTO, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (y.cpu().numpy() == want).all(), np.abs(y.cpu().numpy() - want).max()
+    # tolerance: normal tokens, per-row scale, fp16 out, no bias
+    x = helpers.make_tokens(rng, n, k)
+    want32, _ = p.oracle(np.ascontiguousarray(x.T), use_scale=True)
+    d_x = dev(x)
+    y16 = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")
+    _lib.check(lib.onebit_linear_tokens(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), p.d_scale.data_ptr(), None,
+                                        d_x.data_ptr(), y16.data_ptr(), m, n, k, _lib.OUT_F16, _lib.KERNEL_AUTO, None))
+    _lib.check(lib.onebit_check_device_status())
+    ok, worst = helpers.row_tolerance_ok(y16.cpu().numpy().T, want32)
+    assert ok, worst
+    # the same bits as the reference-convention call on transposed operands (fp32, integer tokens)
+    if m % 256 == 0 and n > 16:
+        ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
+        xi = dev(helpers.make_tokens(rng, n, k, "int"))
+        _lib.check(lib.onebit_matmul_packed(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), None, xi.t().contiguous().data_ptr(),
+                                            ref.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_AUTO, None)) if n % 8 == 0 else None
+        if n % 8 == 0:
+            _lib.check(lib.onebit_linear_tokens(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), None, None, xi.data_ptr(),
+                                                y.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_AUTO, None))
+            assert torch.equal(y, ref.t())
