@@ -33,9 +33,9 @@ enum ObDenseType { OB_DENSE_F16 = 0, OB_DENSE_BF16 = 1, OB_DENSE_I32 = 2 };
 
 // ---- reference-side orders ------------------------------------------------------------------
 
-// Flat uint16 offset of canonical Meta[row][chunk] inside a reference-ordered metadata buffer of
-// an (m x k) matrix; nchunks = k/16 is not needed because the order is column-pair major.
-OB_HD int64_t ob_meta_ref_offset(int dialect, int64_t m, int64_t row, int64_t chunk) {
+// Where canonical Meta[row][chunk] goes in a reference-ordered metadata buffer: shuffled row r and
+// column c, before the column-pair-major linearisation.
+OB_HD void ob_meta_ref_position(int dialect, int64_t row, int64_t chunk, int64_t* r_out, int64_t* c_out) {
   int64_t r;
   if (dialect == OB_META_PYTHON) {
     r = (row / 64) * 64 + (row % 2) * 2 + (row % 8) / 4 + ((row % 4) / 2) * 32 + ((row % 64) / 8) * 4;
@@ -46,7 +46,15 @@ OB_HD int64_t ob_meta_ref_offset(int dialect, int64_t m, int64_t row, int64_t ch
   // 2x2 block swizzle "from Z to N"
   if ((r % 2 == 0) && (c % 2 == 1)) { r += 1; c -= 1; }
   else if ((r % 2 == 1) && (c % 2 == 0)) { r -= 1; c += 1; }
-  // column-major, interleaved by 2 columns
+  *r_out = r;
+  *c_out = c;
+}
+
+// Flat uint16 offset of canonical Meta[row][chunk] inside a reference-ordered metadata buffer of
+// an (m x k) matrix: column-major, interleaved by 2 columns (nchunks = k/16 is not needed).
+OB_HD int64_t ob_meta_ref_offset(int dialect, int64_t m, int64_t row, int64_t chunk) {
+  int64_t r, c;
+  ob_meta_ref_position(dialect, row, chunk, &r, &c);
   return (c / 2) * (2 * m) + r * 2 + (c % 2);
 }
 

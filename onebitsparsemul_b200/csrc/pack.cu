@@ -128,9 +128,9 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
     }
     // reference-ordered metadata: destination stays inside this tile's 4 chunk pairs x 128 rows
     {
-      const int64_t off = ob_meta_ref_offset(a.dialect, a.m, row, chunk);
-      const int64_t pair = off / (2 * a.m), rest = off % (2 * a.m);     // rest = 2*r' + (c' & 1)
-      s_meta_ref[(pair - kb * 4) * 256 + (rest - mb * 256)] = (uint16_t)meta;
+      int64_t rs, cs;                                                   // shuffled row and column
+      ob_meta_ref_position(a.dialect, row, chunk, &rs, &cs);
+      s_meta_ref[(cs / 2 - kb * 4) * 256 + (rs * 2 + (cs & 1) - mb * 256)] = (uint16_t)meta;
     }
   }
   __syncthreads();

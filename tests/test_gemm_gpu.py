@@ -270,3 +270,43 @@ def test_token_major_entry_point(lib, m, n, k):
             _lib.check(lib.onebit_linear_tokens(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), None, None, xi.data_ptr(),
                                                 y.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_AUTO, None))
             assert torch.equal(y, ref.t())
+
+
+# ---- every kernel variant the dispatcher can pick, forced through the tuning knob -----------------------------
+
+_VARIANT_CHILD = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import oracle
+from onebitsparsemul_b200 import _lib
+from tests import helpers
+lib = _lib.load()
+rng = np.random.default_rng(5)
+for (m, n, k) in ((256, 264, 640), (512, 512, 256)):
+    dense, scale = helpers.make_weights(rng, m, k)
+    canon, signs, _ = oracle.compress(dense)
+    bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, 0)
+    bt, mt = helpers.tile_order_from_canonical(canon, signs)
+    B = helpers.make_tokens(rng, k, n, "int")
+    want, _ = oracle.gemm(bits, meta, 0, B, m)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_bt, d_mt, d_b = t(bt), t(mt), t(B)
+    for out_dtype, code in ((torch.float32, _lib.OUT_F32), (torch.float16, _lib.OUT_F16)):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+        _lib.check(lib.onebit_matmul_packed(d_bt.data_ptr(), d_mt.data_ptr(), None, d_b.data_ptr(), out.data_ptr(), m, n, k, code, _lib.KERNEL_PREFILL, None))
+        _lib.check(lib.onebit_check_device_status())
+        assert (out.cpu().numpy() == want.astype(out.cpu().numpy().dtype)).all(), (m, n, k, out_dtype)
+print("variant ok")
+"""
+
+
+@pytest.mark.parametrize("variant", ["121", "1121", "1141", "1221", "2", "22", "1"])
+def test_every_kernel_variant_exact(variant):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ONEBIT_PREFILL_VARIANT=variant)
+    r = subprocess.run([sys.executable, "-c", _VARIANT_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "variant ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
