@@ -411,3 +411,9 @@ cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tma
 }
 
 }  // namespace ob
+
+#ifdef OB_TRACE
+extern "C" int onebit_debug_read_trace2(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace2, sizeof(long long) * 16 * 512);
+}
+#endif

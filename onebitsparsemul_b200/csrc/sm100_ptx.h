@@ -131,9 +131,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// commit the stores issued so far and wait until they have READ their shared-memory source (the
+// buffer may then be reused or the CTA may exit; the global writes complete on their own)
 __device__ __forceinline__ void tma_store_commit_and_wait() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 // ---- CTA-pair (cta_group::2) forms -----------------------------------------------------------------
