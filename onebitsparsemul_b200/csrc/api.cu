@@ -101,7 +101,7 @@ int check_dialect_rows(int dialect, int64_t m) {
 }
 
 int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
-                       int64_t m, int64_t n, int64_t k, int out_type, int kernel, cudaStream_t stream) {
+                       int64_t m, int64_t n, int64_t k, int out_type, int kernel, bool fresh_weights, cudaStream_t stream) {
   if (!bits_tile || !meta_tile || !b || !d) return fail(ONEBIT_ERR_NULL, "null operand pointer");
   if (!tiled_shape(m, k) || n < 1)
     return fail(ONEBIT_ERR_SHAPE, "tile-ordered GEMM needs m %% 128 == 0, k %% 128 == 0, n >= 1 (got m=%lld n=%lld k=%lld)",
@@ -118,7 +118,7 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
     e = ob::launch_gemm_prefill(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, status, stream);
     if (e != cudaSuccess) return cuda_fail(e, "tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, stream);
+    e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, fresh_weights, stream);
     if (e != cudaSuccess) return cuda_fail(e, "decode GEMM launch");
   } else {
     return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
@@ -154,7 +154,7 @@ int onebit_relayout(const void* a_bits, const void* e_meta, int meta_dialect, in
 
 int onebit_matmul_packed(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void* stream) {
-  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, static_cast<cudaStream_t>(stream));
+  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, false, static_cast<cudaStream_t>(stream));
 }
 
 int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias, const void* x,
@@ -209,7 +209,7 @@ int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const vo
   void* meta_tile = static_cast<char*>(workspace) + round256(onebit_packed_bits_bytes(m, k));
   cudaError_t e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
   if (e != cudaSuccess) return cuda_fail(e, "relayout launch");
-  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, st);
+  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, /*fresh_weights=*/true, st);
 }
 
 int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits,
@@ -241,7 +241,7 @@ int onebit_unpack_to_dense(const void* bits_tile, const void* meta_tile, const v
   return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "unpack launch");
 }
 
-// Reads and clears the status word of the tensor-memory kernel on the current device. Synchronises
+// Reads and clears the status words of the tensor-memory and decode kernels on the current device. Synchronises
 // the device. Returns ONEBIT_ERR_DEVICE_WAIT if a bounded wait inside a kernel gave up since the
 // last call.
 int onebit_check_device_status(void) {
@@ -256,6 +256,9 @@ int onebit_check_device_status(void) {
     cudaMemset(status, 0, sizeof(int));
     return fail(ONEBIT_ERR_DEVICE_WAIT, "a bounded wait inside the tensor-memory kernel gave up (role code %d)", host);
   }
+  e = ob::read_decode_status(&host);
+  if (e != cudaSuccess) return cuda_fail(e, "read_decode_status");
+  if (host != 0) return fail(ONEBIT_ERR_DEVICE_WAIT, "a bounded wait inside the decode kernel gave up (code %d)", host);
   return ONEBIT_OK;
 }
 

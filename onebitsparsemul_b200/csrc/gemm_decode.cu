@@ -3,50 +3,89 @@
 //
 // Replaces the reference's 128x64x128 CUTLASS threadblock (csrc/kernel.h:23-25) for the shapes
 // where its 64-wide token tile is almost empty. Such a call moves only a few MiB, so the kernel is
-// built to be short: every weight load of a warp is issued before anything else, and there is one
-// cluster-wide synchronisation in its whole life.
-//   * one CTA = one 128-row block of A x one slice of K, 16 warps: warp w owns rows 16(w%8)..+15 of
-//     half (w/8) of the slice, so a cluster of S CTAs cuts K into 2S slices;
+// built to be short: the whole grid is one wave, every weight byte of a CTA is requested in the
+// first few hundred cycles, and there is at most one cluster-wide synchronisation in its life.
+//   * one CTA = one 128-row block of A x one slice of K (a cluster of S CTAs cuts K into S slices);
+//   * weights: the tile order keeps the metadata (2 KiB) and sign (1 KiB) blocks of consecutive
+//     k tiles of a row block adjacent, so a round of KL tiles is two bulk async copies into a
+//     shared-memory ring. One thread issues the first ring right after initialising the mbarriers
+//     -- 36-48 KiB per CTA in flight before anything else happens -- and refills a slot once all
+//     8 warps have read it (longer slices only);
+//   * 8 warps = RS row sets x KL tile lanes: a warp multiplies RG 16-row groups (64 rows for n <= 8,
+//     32 rows for n <= 16) by ONE tile of the round, so that a token fragment read from shared
+//     memory feeds RG tensor-core instructions; with one row group per warp the kernel was bound by
+//     the shared-memory port, not by HBM;
 //   * the 2:4 gather is done by the tensor core: sign words are expanded in registers to fp16 +-1
 //     pairs (one shift + one logic op per pair, see the tile order in formats.h) and fed with the
 //     metadata words to mma.sp m16n8k32 with fp32 accumulation;
-//   * tokens (B, k x n row-major) are staged TRANSPOSED in shared memory (one padded row per token,
-//     zero rows beyond n) by the half that uses them (named barrier per half), so that a B fragment
-//     register is one 32-bit load;
-//   * split-K reduction: every warp PUSHES its partial sums through distributed shared memory into
-//     the CTA that owns those output rows; after the single cluster barrier each CTA sums its 2S
-//     slices in a fixed order from its own shared memory, scales, converts and stores. No atomics,
-//     no scratch in HBM, no remote reads, deterministic.
+//   * tokens (B, k x n row-major, or x, n x k row-major) are staged TRANSPOSED in shared memory (one
+//     padded row per token and tile; columns beyond n read one shared row of zeros), so that a B
+//     fragment register is one 32-bit load; the global loads of all rounds in the ring are issued together;
+//   * reduction: the KL partial sums of a CTA are added through shared memory (the drained weight
+//     ring); with S > 1 every thread then PUSHES 16 bytes of sums through distributed shared memory into
+//     the CTA that owns those output rows (remote stores are slow to issue: one per thread), and after
+//     the single cluster barrier each CTA adds the S slices in a fixed order, scales, converts and
+//     stores. No atomics, no scratch in HBM, no remote reads, deterministic;
+//   * programmatic dependent launch: the grid may start while the previous kernel of the stream
+//     drains. Packed weights are long-lived, so their loads go out first; the tokens are read, and
+//     global memory is written, only after griddepcontrol.wait.
+// Every mbarrier wait is bounded; a wait that gives up records a code in g_decode_status.
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <climits>
 #include <cstdlib>
 
 #include "formats.h"
 #include "kernels.h"
+#include "sm100_ptx.h"
 
 namespace cg = cooperative_groups;
 
 namespace {
 
+using ob_ptx::expand_pair;
+
 // Timeline instrumentation for tuning, compiled in only with -DOB_TRACE.
 #ifdef OB_TRACE
 __device__ long long g_trace_dec[4][16];
-#define OB_TRACE_EV(ev) do { if (blockIdx.x == 3 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == 511) && blockIdx.y < 2) g_trace_dec[blockIdx.y * 2 + (threadIdx.x != 0)][ev] = clock64(); } while (0)
+#define OB_TRACE_EV(ev) do { if (blockIdx.x == 3 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == blockDim.x - 1) && blockIdx.y < 2) g_trace_dec[blockIdx.y * 2 + (threadIdx.x != 0)][ev] = clock64(); } while (0)
 #else
 #define OB_TRACE_EV(ev) do { } while (0)
 #endif
 
-constexpr int kChunkTiles = 3;                       // tiles (128 k each) of one warp in flight together
-constexpr int kChunkK = kChunkTiles * OB_TILE_K;     // 384
-constexpr int kMaxSlices = 16;                       // 2 halves x cluster of up to 8
-constexpr int kBtStride = kChunkK + 8;               // halves per token column; +8 skews the columns over the banks
+// nonzero once a bounded wait has given up (100 + role code); read and cleared by the host
+__device__ int g_decode_status;
 
-__device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
-  // bits j and 16+j of w -> fp16x2 {bit ? +1 : -1}
-  return ((w << (15 - j)) & 0x80008000u) ^ 0xBC00BC00u;
-}
+constexpr int kTileBytes = OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
+constexpr int kTokStride = OB_TILE_K + 8;            // halves per token row of one tile; +8 skews the rows over the banks
+
+// geometry and dynamic shared memory of one CTA; two CTAs share an SM
+template <int NT> struct DecodeCfg {
+  static constexpr int NP = NT * 8;                                           // token columns per pass
+  // 8 warps; two CTAs share an SM, which leaves each thread 128 registers. (16 warps of 64 registers
+  // were slower: the sign expansion is integer-ALU work that more warps do not speed up, and they spill.)
+  static constexpr int kThreads = 256;
+  static constexpr int RG = 4;                                                // 16-row groups per warp (64 rows)
+  static constexpr int RS = 8 / RG;                                           // row sets per CTA
+  static constexpr int KL = (kThreads / 32) / RS;                             // tile lanes = tiles per round
+  static constexpr int kRing = (NT == 1) ? 4 : 3;                             // rounds in flight
+  static constexpr int kPieces = KL * OB_TILE_K * NP / 8 / kThreads;          // 16-byte token pieces per thread and round
+  static constexpr int kRoundWeights = KL * kTileBytes;                       // [meta of KL tiles | signs of KL tiles]
+  static constexpr int kTileTokens = NP * kTokStride * 2;                     // one tile's tokens, transposed
+  static constexpr int kRoundTokens = KL * kTileTokens;
+  static constexpr int kWeights = kRing * kRoundWeights;
+  static constexpr int kTokens = kRing * kRoundTokens;
+  static constexpr int kRecv = 128 * NP * 4;                                  // [source rank][row of this CTA's share][token]
+  static constexpr int kRed = KL * 128 * NP * 4;                              // [tile lane][row][token], reuses the drained ring
+  static_assert(kRed <= kWeights + kTokens, "the reduction buffer must fit the drained ring");
+  static constexpr int kBars = 2 * kRing * 8;                                 // [full | empty][slot]
+  static constexpr int kZeroRow = (kTokStride * 2 + 15) / 16 * 16;            // a token row of zeros
+  static constexpr int kTotal = kWeights + kTokens + kRecv + kBars + kZeroRow;
+  static_assert(2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM must fit");
+  static_assert(KL * OB_TILE_K * NP / 8 == kPieces * kThreads, "a round's tokens are whole 16-byte pieces per thread");
+};
 
 __device__ __forceinline__ void mma_sp_16832(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[4],
                                              uint32_t e) {
@@ -57,21 +96,6 @@ __device__ __forceinline__ void mma_sp_16832(float (&d)[4], const uint32_t (&a)[
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(e));
 }
 
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint2 ld_stream8(const void* p) {
-  uint2 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void half_barrier(int half) {      // the 256 threads of one half of the CTA
-  asm volatile("bar.sync %0, 256;" ::"r"(half + 1) : "memory");
-}
-
 struct DecodeArgs {
   const uint8_t* bits_tile;
   const uint8_t* meta_tile;
@@ -80,15 +104,16 @@ struct DecodeArgs {
   const __half* b;
   void* d;
   int64_t m, n, k;
+  int fresh_weights;    // 1: the weight buffers were written by the kernel launched just before this one
 };
 
 // NT = number of 8-token tiles per pass (1 or 2)
 // TM = token-major operands (the nn.Linear convention): b is x (n, k) row-major, d is y (n, m) row-major
 template <int NT, typename OutT, bool TM>
-__global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
-  constexpr int NP = NT * 8;
-  __shared__ __align__(16) __half s_b[2][NP * kBtStride];          // per half: s_b[j][kk] = B[k0 + kk][n0 + j]
-  __shared__ __align__(16) float s_recv[kMaxSlices * 16 * NP];    // [slice][row of this CTA's share][token]
+__global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_kernel(DecodeArgs a) {
+  using L = DecodeCfg<NT>;
+  constexpr int NP = L::NP, RG = L::RG, RS = L::RS, KL = L::KL, kRing = L::kRing, kPieces = L::kPieces, kThreads = L::kThreads;
+  extern __shared__ __align__(128) uint8_t smem[];
 
   OB_TRACE_EV(0);
   // the cluster spans the whole y extent of the grid: rank and size come from the launch geometry,
@@ -97,144 +122,274 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
   const int rank = (int)blockIdx.y;
   const int64_t mb = blockIdx.x;
   const int64_t n0 = (int64_t)blockIdx.z * NP;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int half = warp >> 3, w8 = warp & 7;                  // K half, 16-row block
-  const int tid_h = threadIdx.x & 255;                        // thread index inside the half
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rs = warp % RS, kl = warp / RS;                   // row set, tile lane
   const int g = lane >> 2, t = lane & 3;
 
-  const int64_t tiles_k = a.k / OB_TILE_K;
-  const int slices = 2 * S, slice = 2 * rank + half;
-  const int64_t tile_begin = tiles_k * slice / slices, tile_end = tiles_k * (slice + 1) / slices;
+  uint8_t* wring = smem;
+  __half* stok = reinterpret_cast<__half*>(smem + L::kWeights);
+  float* s_recv = reinterpret_cast<float*>(smem + L::kWeights + L::kTokens);
+  const uint32_t bar0 = ob_ptx::smem_u32(smem + L::kWeights + L::kTokens + L::kRecv);
+  const __half* zrow = reinterpret_cast<const __half*>(smem + L::kWeights + L::kTokens + L::kRecv + L::kBars);
+  if (tid < L::kZeroRow / 16) reinterpret_cast<uint4*>(smem + L::kWeights + L::kTokens + L::kRecv + L::kBars)[tid] = make_uint4(0, 0, 0, 0);
+  auto bar_full = [&](int s) { return bar0 + 8 * s; };
+  auto bar_empty = [&](int s) { return bar0 + 8 * (kRing + s); };
 
-  const int u = g + 8 * (t & 1) + 16 * w8;                    // metadata lane of this thread
-  const int row_lo = 16 * w8 + g;
+  const int tiles_k = (int)(a.k / OB_TILE_K);
+  const int tile_begin = (int)((int64_t)tiles_k * rank / S), tile_end = (int)((int64_t)tiles_k * (rank + 1) / S);
+  const int T = tile_end - tile_begin;                        // tiles of this CTA's slice
+  const int nrounds = (T + KL - 1) / KL;
+  long long budget = 2000000000ll;
 
-  // 1. the weight loads of the first chunk, before anything else
-  uint4 meta[kChunkTiles];
-  uint2 blo[kChunkTiles], bhi[kChunkTiles];
-  auto load_chunk = [&](int64_t chunk) {
-#pragma unroll
-    for (int ti = 0; ti < kChunkTiles; ++ti) {
-      if (chunk + ti < tile_end) {
-        const int64_t tile = mb * tiles_k + chunk + ti;
-        meta[ti] = ld_stream16(a.meta_tile + tile * OB_TILE_META_BYTES + u * 16);
-        blo[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + row_lo * 8);
-        bhi[ti] = ld_stream8(a.bits_tile + tile * OB_TILE_BITS_BYTES + (row_lo + 8) * 8);
-      }
-    }
+  // 1. the weight stream: round r of the slice -> ring slot r % kRing
+  auto issue = [&](int r) {
+    const int s = r % kRing;
+    const int nt = min(KL, T - r * KL);
+    const int64_t tile = mb * tiles_k + tile_begin + r * KL;
+    const uint32_t dst = ob_ptx::smem_u32(wring + s * L::kRoundWeights);
+    ob_ptx::mbar_expect_tx(bar_full(s), nt * kTileBytes);
+    ob_ptx::bulk_load(dst, a.meta_tile + tile * OB_TILE_META_BYTES, nt * OB_TILE_META_BYTES, bar_full(s));
+    ob_ptx::bulk_load(dst + KL * OB_TILE_META_BYTES, a.bits_tile + tile * OB_TILE_BITS_BYTES, nt * OB_TILE_BITS_BYTES, bar_full(s));
   };
-  load_chunk(tile_begin);
+  if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (tid == 0) {
+    for (int s = 0; s < kRing; ++s) { ob_ptx::mbar_init(bar_full(s), 1); ob_ptx::mbar_init(bar_empty(s), kThreads / 32); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const int npre = min(nrounds, kRing);
+    for (int r = 0; r < npre; ++r) issue(r);
+  }
+  __syncwarp();
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may begin its own prologue
+  asm volatile("griddepcontrol.wait;" ::: "memory");                // the previous kernel's results (the tokens) are complete
   OB_TRACE_EV(1);
 
-  // two independent accumulation chains per token tile (even / odd k-blocks): the warp-level MMA has
-  // a long latency and a single chain would serialise on it
-  float acc[2][NT][4];
+  float acc[RG][NT][4];
 #pragma unroll
-  for (int c = 0; c < 2; ++c)
+  for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[c][nt][i] = 0.f;
+      for (int i = 0; i < 4; ++i) acc[rg][nt][i] = 0.f;
 
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
-  const bool vec_rows = !TM && (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
-  __half* sb = s_b[half];
+  // one token (n == 1) in the reference layout is the same contiguous vector as a token-major row
+  const bool rows_contiguous = TM || a.n == 1;
+  const bool vec_rows = !rows_contiguous && (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
 
-  for (int64_t chunk = tile_begin; chunk < tile_end; chunk += kChunkTiles) {
-    const int ntile = (int)min((int64_t)kChunkTiles, tile_end - chunk);
-    if (chunk != tile_begin) {
-      half_barrier(half);                                     // previous chunk's readers are done
-      load_chunk(chunk);
-    }
-    // 2. tokens of the chunk: sb[kk][j] = B[k0 + kk][n0 + j], zero beyond n
-    const int64_t k0 = chunk * OB_TILE_K;
-    const int kc = ntile * OB_TILE_K;
-    if constexpr (TM) {
-      // token j is a contiguous row of x: 16-byte pieces along k, zero rows beyond n
-      const int pieces = kc / 8;
-      for (int idx = tid_h; idx < NP * pieces; idx += 256) {
-        const int j = idx / pieces, pc = idx - j * pieces;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (j < nvalid) v = __ldg(reinterpret_cast<const uint4*>(a.b + (n0 + j) * a.k + k0 + pc * 8));
-        *reinterpret_cast<uint4*>(&sb[j * kBtStride + pc * 8]) = v;
-      }
-    } else if (vec_rows) {
-      constexpr int kPieces = NP / 8;                         // 16-byte pieces per token row
-      for (int idx = tid_h; idx < kc * kPieces; idx += 256) {
-        const int kk = idx / kPieces, pc = idx % kPieces;
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
-        const __half* h = reinterpret_cast<const __half*>(&v);
+  // 2. tokens of one round: at most two 16-byte pieces per thread, fetched into registers, then scattered
+  //    into tok[slot][tile][j][kk] = B[k0 + 128 tile + kk][n0 + j]. Rows j >= nvalid are never written.
+  auto fetch_tokens = [&](int r, uint4 (&tv)[kPieces]) {
+    const int ntile = min(KL, T - r * KL);
+    const int64_t k0 = (int64_t)(tile_begin + r * KL) * OB_TILE_K;
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) sb[(pc * 8 + jj) * kBtStride + kk] = h[jj];
-      }
-    } else {
-      for (int kk = tid_h; kk < kc; kk += 256) {
+    for (int i = 0; i < kPieces; ++i) {
+      tv[i] = make_uint4(0, 0, 0, 0);
+      const int idx = tid + kThreads * i;
+      if (rows_contiguous) {
+        // token j is contiguous along k: 16 pieces of 8 values per tile
+        const int j = idx / (KL * 16), pc = idx % (KL * 16);
+        if (j < nvalid && (pc >> 4) < ntile) tv[i] = __ldg(reinterpret_cast<const uint4*>(a.b + (n0 + j) * a.k + k0 + pc * 8));
+      } else {
+        const int kk = idx / NT, pc = idx % NT;               // k-row of the round, 8-token piece of that row
+        if ((kk >> 7) < ntile) {
+          if (vec_rows) {
+            tv[i] = __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
+          } else {
+            __half* h = reinterpret_cast<__half*>(&tv[i]);
 #pragma unroll
-        for (int j = 0; j < NP; ++j) sb[j * kBtStride + kk] = (j < nvalid) ? a.b[(k0 + kk) * a.n + n0 + j] : __float2half(0.f);
-      }
-    }
-    OB_TRACE_EV(2);
-    half_barrier(half);
-    OB_TRACE_EV(3);
-
-    // 3. four mma.sp per tile and token tile
-#pragma unroll
-    for (int ti = 0; ti < kChunkTiles; ++ti) {
-      if (ti < ntile) {
-        const uint32_t mw[4] = {meta[ti].x, meta[ti].y, meta[ti].z, meta[ti].w};
-        const uint32_t wl[2] = {blo[ti].x, blo[ti].y}, wh[2] = {bhi[ti].x, bhi[ti].y};
-#pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-          const int j1 = 8 * (kb & 1) + t, j2 = j1 + 4;
-          uint32_t af[4];
-          af[0] = expand_pair(wl[kb >> 1], j1);
-          af[1] = expand_pair(wh[kb >> 1], j1);
-          af[2] = expand_pair(wl[kb >> 1], j2);
-          af[3] = expand_pair(wh[kb >> 1], j2);
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            // fragment register i: token column nt*8+g, k rows 2t+8i and 2t+8i+1 of the k-block
-            const uint32_t* brow = reinterpret_cast<const uint32_t*>(sb + (nt * 8 + g) * kBtStride + ti * OB_TILE_K + kb * 32);
-            uint32_t bf[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) bf[i] = brow[t + 4 * i];
-            mma_sp_16832(acc[kb & 1][nt], af, bf, mw[kb]);
+            for (int jj = 0; jj < 8; ++jj)
+              if (8 * pc + jj < nvalid) h[jj] = a.b[(k0 + kk) * a.n + n0 + 8 * pc + jj];
           }
         }
+      }
+    }
+  };
+  auto store_tokens = [&](int r, const uint4 (&tv)[kPieces]) {
+    const int ntile = min(KL, T - r * KL);
+    __half* sb = stok + (r % kRing) * (KL * NP * kTokStride);
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i) {
+      const int idx = tid + kThreads * i;
+      if (rows_contiguous) {
+        const int j = idx / (KL * 16), pc = idx % (KL * 16);
+        if (j < nvalid && (pc >> 4) < ntile) *reinterpret_cast<uint4*>(&sb[((pc >> 4) * NP + j) * kTokStride + (pc & 15) * 8]) = tv[i];
+      } else {
+        const int kk = idx / NT, pc = idx % NT;
+        const __half* h = reinterpret_cast<const __half*>(&tv[i]);
+        if ((kk >> 7) < ntile) {
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj)
+            if (8 * pc + jj < nvalid) sb[((kk >> 7) * NP + pc * 8 + jj) * kTokStride + (kk & 127)] = h[jj];
+        }
+      }
+    }
+  };
+
+  // a span = the rounds that fit the ring; most decode shapes are a single span
+  for (int r0 = 0; r0 < nrounds; r0 += kRing) {
+    if (r0 > 0) __syncthreads();                              // the previous span's token buffers are free
+    {
+      uint4 tv[kRing][kPieces];
+#pragma unroll
+      for (int ri = 0; ri < kRing; ++ri)
+        if (r0 + ri < nrounds) fetch_tokens(r0 + ri, tv[ri]);
+#pragma unroll
+      for (int ri = 0; ri < kRing; ++ri)
+        if (r0 + ri < nrounds) store_tokens(r0 + ri, tv[ri]);
+    }
+    if (r0 == 0) OB_TRACE_EV(2);
+    __syncthreads();                                          // tokens staged (and, first time, the mbarriers exist)
+    if (r0 == 0) OB_TRACE_EV(3);
+
+#pragma unroll 1
+    for (int r = r0; r < min(nrounds, r0 + kRing); ++r) {
+      const int s = r - r0;
+      // every warp waits for every round: afterwards no copy of the slot is in flight
+      ob_ptx::mbar_wait(bar_full(s), (r / kRing) & 1, budget, &g_decode_status, 101);
+      if (r < 4) OB_TRACE_EV(8 + 2 * r);
+
+      // 3. this warp's tile of the round: per 32-k block one token fragment feeds RG mma.sp
+      if (r * KL + kl < T) {
+        const uint8_t* wmeta = wring + s * L::kRoundWeights + kl * OB_TILE_META_BYTES;
+        const uint8_t* wbits = wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + kl * OB_TILE_BITS_BYTES;
+        const __half* sb = stok + (s * KL + kl) * (NP * kTokStride);
+        // this thread's token rows; columns beyond n read the zero row (their buffer rows are never written)
+        const __half* trow[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) trow[nt] = (nt * 8 + g < nvalid) ? sb + (nt * 8 + g) * kTokStride : zrow;
+#pragma unroll
+        for (int p = 0; p < 2; ++p) {                         // pairs of 32-k blocks: one sign word per row
+          uint32_t bf[2][NT][4];
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              // fragment register i: token column nt*8+g, k rows 2t+8i and 2t+8i+1 of the 32-k block
+              const uint32_t* brow = reinterpret_cast<const uint32_t*>(trow[nt] + (2 * p + q) * 32);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) bf[q][nt][i] = brow[t + 4 * i];
+            }
+          // RGC row groups at a time; consecutive MMAs go to different accumulators, so the next one
+          // does not wait for the previous one
+          constexpr int RGC = RG;
+#pragma unroll
+          for (int r0g = 0; r0g < RG; r0g += RGC) {
+            uint2 mw[RGC];
+            uint32_t wl[RGC], wh[RGC];
+#pragma unroll
+            for (int c = 0; c < RGC; ++c) {
+              const int grp = rs * RG + r0g + c;              // 16-row group of the tile
+              const int u = g + 8 * (t & 1) + 16 * grp;       // metadata lane of this thread
+              mw[c] = *reinterpret_cast<const uint2*>(wmeta + u * 16 + p * 8);
+              wl[c] = *reinterpret_cast<const uint32_t*>(wbits + (16 * grp + g) * 8 + p * 4);
+              wh[c] = *reinterpret_cast<const uint32_t*>(wbits + (16 * grp + g + 8) * 8 + p * 4);
+            }
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+              for (int c = 0; c < RGC; ++c) {
+                const int j1 = 8 * q + t, j2 = j1 + 4;
+                const uint32_t af[4] = {expand_pair(wl[c], j1), expand_pair(wh[c], j1), expand_pair(wl[c], j2), expand_pair(wh[c], j2)};
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_sp_16832(acc[r0g + c][nt], af, bf[q][nt], q ? mw[c].y : mw[c].x);
+              }
+          }
+        }
+      }
+      if (r < 4) OB_TRACE_EV(9 + 2 * r);
+      // a slice longer than the ring: hand the weight slot back and refill it for the next span
+      if (r + kRing < nrounds) {
+        __syncwarp();
+        if (lane == 0) ob_ptx::mbar_arrive(bar_empty(s));
+        if (tid == 0) {
+          ob_ptx::mbar_wait(bar_empty(s), (r / kRing) & 1, budget, &g_decode_status, 102);
+          issue(r + kRing);
+        }
+        __syncwarp();
       }
     }
   }
 
   OB_TRACE_EV(4);
-  // 4. push the partial sums to the CTA that owns the rows: CTA r owns rows [r * 128/S, (r+1) * 128/S)
-  cg::cluster_group cluster = cg::this_cluster();
-  const int rows_per = 128 / S;
+  // 4. the KL partial sums of the CTA meet in shared memory: the ring is drained (every warp has seen
+  //    every round land), so it serves as the buffer red[tile lane][row][token]
+  __syncthreads();
+  float* red = reinterpret_cast<float*>(smem);
 #pragma unroll
-  for (int hrow = 0; hrow < 2; ++hrow) {
-    const int r = row_lo + 8 * hrow;
-    float* dst = cluster.map_shared_rank(s_recv, r / rows_per) + (slice * rows_per + (r % rows_per)) * NP;
+  for (int rg = 0; rg < RG; ++rg)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-      *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(acc[0][nt][2 * hrow] + acc[1][nt][2 * hrow],
-                                                                   acc[0][nt][2 * hrow + 1] + acc[1][nt][2 * hrow + 1]);
-  }
-  OB_TRACE_EV(5);
-  cluster.sync();                                             // the only cluster-wide barrier
-  OB_TRACE_EV(6);
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      const int row = (rs * RG + rg) * 16 + g + 8 * hrow;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+        *reinterpret_cast<float2*>(&red[(kl * 128 + row) * NP + nt * 8 + 2 * t]) = make_float2(acc[rg][nt][2 * hrow], acc[rg][nt][2 * hrow + 1]);
+    }
+  __syncthreads();
 
-  // 5. fixed-order sum of the 2S slices from this CTA's own shared memory
-  for (int e = threadIdx.x; e < rows_per * NP; e += 512) {
-    // consecutive threads walk the fastest output dimension: tokens of a row (m x n), rows of a token (n x m)
-    const int rr = TM ? e % rows_per : e / NP, j = TM ? e / rows_per : e % NP;
-    float sum = 0.f;
-    for (int sl = 0; sl < slices; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
-    const int64_t row = mb * 128 + rank * rows_per + rr;
-    if (a.scale) sum *= __half2float(a.scale[row]);
-    if (a.bias) sum += __half2float(a.bias[row]);
+  auto finish = [&](int64_t row, int j, float sum, float scale, float bias) {
+    sum = __fmul_rn(sum, scale);                              // two roundings, like the other kernels' epilogues
+    if (a.bias) sum = __fadd_rn(sum, bias);
     if (j < nvalid) {
       const int64_t o = TM ? (n0 + j) * a.m + row : row * a.n + n0 + j;
       if constexpr (sizeof(OutT) == 2) static_cast<__half*>(a.d)[o] = __float2half_rn(sum);
       else static_cast<float*>(a.d)[o] = sum;
+    }
+  };
+  // each thread adds the lanes for NT groups of four consecutive tokens of one row
+  constexpr int kQuads = 128 * NP / 4;                        // = NT * kThreads
+  const int rows_per = 128 / S;                               // S is a power of two
+  cg::cluster_group cluster = cg::this_cluster();
+#pragma unroll
+  for (int i = 0; i < kQuads / kThreads; ++i) {
+    const int x = tid + i * kThreads;
+    float4 v = *reinterpret_cast<const float4*>(&red[4 * x]);
+#pragma unroll
+    for (int l = 1; l < KL; ++l) {
+      const float4 w = *reinterpret_cast<const float4*>(&red[l * 128 * NP + 4 * x]);
+      v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    const int row = 4 * x / NP, j = 4 * x % NP;
+    if (S == 1) {
+      // no other CTA shares these rows
+      const int64_t grow = mb * 128 + row;
+      const float scale = a.scale ? __half2float(a.scale[grow]) : 1.f, bias = a.bias ? __half2float(a.bias[grow]) : 0.f;
+      finish(grow, j, v.x, scale, bias); finish(grow, j + 1, v.y, scale, bias);
+      finish(grow, j + 2, v.z, scale, bias); finish(grow, j + 3, v.w, scale, bias);
+    } else {
+      // 5. one 16-byte push to the CTA that owns the row: CTA q of the cluster owns rows [q * 128/S, (q+1) * 128/S)
+      float* dst = cluster.map_shared_rank(s_recv, row / rows_per) + ((rank * rows_per + row % rows_per) * NP + j);
+      *reinterpret_cast<float4*>(dst) = v;
+    }
+  }
+  if (S == 1) { OB_TRACE_EV(7); return; }
+  OB_TRACE_EV(5);
+  // the per-row constants of this thread's outputs, fetched while the barrier is pending
+  constexpr int kOut = (128 * NP / 2 + kThreads - 1) / kThreads;   // outputs per thread at S = 2, the most
+  float sc[kOut], bs[kOut];
+#pragma unroll
+  for (int i = 0; i < kOut; ++i) {
+    const int e = tid + i * kThreads;
+    sc[i] = 1.f; bs[i] = 0.f;
+    if (e < rows_per * NP) {
+      const int rr = TM ? e % rows_per : e / NP;
+      const int64_t row = mb * 128 + rank * rows_per + rr;
+      if (a.scale) sc[i] = __half2float(a.scale[row]);
+      if (a.bias) bs[i] = __half2float(a.bias[row]);
+    }
+  }
+  cluster.sync();                                             // the only cluster-wide barrier
+  OB_TRACE_EV(6);
+
+  // 6. fixed-order sum of the S slices from this CTA's own shared memory
+#pragma unroll
+  for (int i = 0; i < kOut; ++i) {
+    const int e = tid + i * kThreads;
+    if (e < rows_per * NP) {
+      // consecutive threads walk the fastest output dimension: tokens of a row (m x n), rows of a token (n x m)
+      const int rr = TM ? e % rows_per : e / NP, j = TM ? e / rows_per : e % NP;
+      float sum = 0.f;
+      for (int sl = 0; sl < S; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
+      finish(mb * 128 + rank * rows_per + rr, j, sum, sc[i], bs[i]);
     }
   }
   OB_TRACE_EV(7);
@@ -242,18 +397,32 @@ __global__ void __launch_bounds__(512, 2) ob_gemm_decode_kernel(DecodeArgs a) {
 
 template <int NT, typename OutT, bool TM>
 cudaError_t launch(const DecodeArgs& a, int S, cudaStream_t stream) {
+  using L = DecodeCfg<NT>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_decode_kernel<NT, OutT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(a.m / 128), (unsigned)S, (unsigned)((a.n + NT * 8 - 1) / (NT * 8)));
-  cfg.blockDim = dim3(512);
-  cfg.dynamicSmemBytes = 0;
+  cfg.blockDim = dim3(L::kThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = (unsigned)S;
   attr[0].val.clusterDim.z = 1;
+  // let this grid start while the previous kernel of the stream drains (ONEBIT_PDL=0 turns it off)
+  static const bool pdl = [] { const char* v = getenv("ONEBIT_PDL"); return !(v && atoi(v) == 0); }();
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, ob_gemm_decode_kernel<NT, OutT, TM>, a);
 }
 
@@ -262,30 +431,36 @@ cudaError_t launch(const DecodeArgs& a, int S, cudaStream_t stream) {
 namespace ob {
 
 namespace {
-int pick_split(int64_t m, int64_t k) {
-  // split K over a cluster of up to 8 CTAs (16 slices), as far as there are tiles and until the
-  // grid holds about two CTAs per SM
+// K split over a cluster of S CTAs. A CTA multiplies its slice in rounds of `lanes` tiles, and an SM
+// holds two CTAs: S minimises rounds x CTAs per SM among the splits that keep the grid one wave.
+int pick_split(int64_t m, int64_t k, int lanes) {
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
-  int S = 1;
-  while (S < 8 && 4 * S <= tiles_k && row_blocks * S < 2 * 148) S *= 2;
+  int best = 1;
+  long long best_cost = LLONG_MAX;
+  for (int S = 1; S <= 8; S *= 2) {
+    if (S > 1 && (row_blocks * S > 2 * 148 || tiles_k < S)) break;
+    const long long T = (tiles_k + S - 1) / S, rounds = (T + lanes - 1) / lanes, per_sm = (row_blocks * S + 147) / 148;
+    if (rounds * per_sm <= best_cost) { best = S; best_cost = rounds * per_sm; }   // ties: more CTAs stream
+  }
   // tuning knob for experiments
   static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_SPLIT"); return v ? atoi(v) : 0; }();
-  if (forced == 1 || forced == 2 || forced == 4 || forced == 8) S = forced;
-  return S;
+  if ((forced == 1 || forced == 2 || forced == 4 || forced == 8) && forced <= tiles_k) best = forced;
+  return best;
 }
 template <bool TM>
 cudaError_t dispatch(const DecodeArgs& a, int out_type, cudaStream_t stream) {
-  const int S = pick_split(a.m, a.k);
   const bool two = (a.n > 8);
+  const int S = pick_split(a.m, a.k, two ? DecodeCfg<2>::KL : DecodeCfg<1>::KL);
   if (out_type == OB_OUT_F16) return two ? launch<2, __half, TM>(a, S, stream) : launch<1, __half, TM>(a, S, stream);
   return two ? launch<2, float, TM>(a, S, stream) : launch<1, float, TM>(a, S, stream);
 }
 }  // namespace
 
 cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
-                               void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream) {
+                               void* d, int64_t m, int64_t n, int64_t k, int out_type, bool fresh_weights,
+                               cudaStream_t stream) {
   DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-               static_cast<const __half*>(scale), nullptr, static_cast<const __half*>(b), d, m, n, k};
+               static_cast<const __half*>(scale), nullptr, static_cast<const __half*>(b), d, m, n, k, fresh_weights ? 1 : 0};
   return dispatch<false>(a, out_type, stream);
 }
 
@@ -293,8 +468,16 @@ cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_ti
                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
                                       cudaStream_t stream) {
   DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(x), y, m, n, k};
+               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(x), y, m, n, k, 0};
   return dispatch<true>(a, out_type, stream);
+}
+
+// Reads and clears the decode kernel's wait status on the current device (0 = no wait gave up).
+cudaError_t read_decode_status(int* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_decode_status, sizeof(int));
+  if (e != cudaSuccess || *out == 0) return e;
+  const int zero = 0;
+  return cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
 }
 
 }  // namespace ob

@@ -327,6 +327,17 @@ cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tma
                                  const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                  void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
                                  cudaStream_t stream);
+bool prefill3_supported(int64_t m, int64_t n, int64_t k, int out_type, const void* d, bool token_major);
+cudaError_t launch_gemm_prefill3(const CUtensorMap* tmap, bool token_major, const void* bits_tile, const void* meta_tile,
+                                 const void* scale, const void* bias, void* d, int64_t m, int64_t n, int64_t k, int* status,
+                                 cudaStream_t stream);
+
+namespace {
+int forced_variant() {
+  static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
+  return forced;
+}
+}  // namespace
 
 bool prefill_supported(int64_t m, int64_t n, int64_t k) {
   return m % BM == 0 && k % BK == 0 && n % 8 == 0 && n >= 8 && k >= BK;
@@ -351,14 +362,19 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   // Tuning knob for experiments: ONEBIT_PREFILL_VARIANT = 121 (single CTA, +-1 operand expanded into
   // shared memory: the first version of this kernel, kept as the baseline of the profiling history),
   // 1121 / 1141 / 1221 (single CTA, operand in tensor memory: 128 tokens / 256 tokens / two stacked
-  // weight tiles), 2 / 22 (CTA-pair kernel with one / two weight tiles per stage), 1 (shape heuristic
-  // without the CTA-pair kernel).
-  static const int forced = [] { const char* v = getenv("ONEBIT_PREFILL_VARIANT"); return v ? atoi(v) : 0; }();
+  // weight tiles), 2 / 22 (CTA-pair kernel with one / two weight tiles per stage), 3 (persistent CTA-pair
+  // kernel), 1 (shape heuristic without the CTA-pair kernels).
+  const int forced = forced_variant();
   const int64_t row_tiles = m / BM;
   const bool two = (m % 256 == 0);
   // The CTA-pair kernel (256 rows x 256 tokens per pair, each CTA staging half of the token tile) is
   // the fastest once its pairs fill the 74 SM pairs.
   const bool pair_fits = n > 128 && prefill2_supported(m, n, k) && (row_tiles / 2) * ((n + 255) / 256) >= 74;
+  if (forced == 3 && prefill3_supported(m, n, k, out_type, d, false)) {
+    CUtensorMap tmap3;
+    if (!make_map(&tmap3, BK * 2)) return cudaErrorInvalidValue;
+    return launch_gemm_prefill3(&tmap3, false, bits_tile, meta_tile, scale, nullptr, d, m, n, k, status, stream);
+  }
   if (((forced == 2 || forced == 22) && prefill2_supported(m, n, k)) || (forced == 0 && pair_fits)) {
     const int ks = (forced == 2) ? 1 : 2;
     CUtensorMap tmap2, tmap_c;
@@ -417,6 +433,8 @@ cudaError_t launch_gemm_prefill_tokens(const void* bits_tile, const void* meta_t
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
+  if (forced_variant() == 3 && prefill3_supported(m, n, k, out_type, y, true))
+    return launch_gemm_prefill3(&tmap_x, true, bits_tile, meta_tile, scale, bias, y, m, n, k, status, stream);
   bool y_map = false;
   if (out_type == OB_OUT_F16 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
     const cuuint64_t dims[2] = {(cuuint64_t)m, (cuuint64_t)n};

@@ -21,9 +21,11 @@ cudaError_t launch_tile_to_dense(const void* bits_tile, const void* meta_tile, c
 cudaError_t launch_gemm_simple(const void* bits_ref, const void* meta_ref, int dialect, const void* scale,
                                const void* b, void* d, int64_t m, int64_t n, int64_t k, int out_type,
                                cudaStream_t stream);
-// K3: decode kernel, n small (gemm_decode.cu). tile-ordered operands.
+// K3: decode kernel, n small (gemm_decode.cu). tile-ordered operands. fresh_weights: the weight buffers were
+// written by the kernel launched just before on the same stream (the kernel then loads nothing before that one is done).
 cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
-                               void* d, int64_t m, int64_t n, int64_t k, int out_type, cudaStream_t stream);
+                               void* d, int64_t m, int64_t n, int64_t k, int out_type, bool fresh_weights,
+                               cudaStream_t stream);
 // K2: tcgen05 kernel (gemm_prefill_sm100.cu). tile-ordered operands; n % 8 == 0.
 // status: device word that receives a non-zero code if a bounded wait inside the kernel gave up.
 cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
@@ -38,5 +40,7 @@ bool prefill_tokens_supported(int64_t m, int64_t n, int64_t k);
 cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
                                       cudaStream_t stream);
+// Reads and clears the decode kernel's bounded-wait status on the current device (0 = nothing gave up).
+cudaError_t read_decode_status(int* out);
 
 }  // namespace ob

@@ -88,7 +88,7 @@ extern "C" int onebit_sparse_matmul_static(const void* a_bits, const void* b, vo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
   if (e != cudaSuccess) return fail(ONEBIT_ERR_CUDA, cudaGetErrorString(e));
-  e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, st);
+  e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, /*fresh_weights=*/true, st);
   if (e != cudaSuccess) return fail(ONEBIT_ERR_CUDA, cudaGetErrorString(e));
   return ONEBIT_OK;
 }

@@ -101,6 +101,10 @@ def trace_decode(m, n, k):
     names = ["start", "weight loads issued", "tokens staged", "half barrier", "MMAs done", "partials pushed", "cluster barrier", "stored"]
     for i, who in enumerate(["CTA 0 thread 0", "CTA 0 thread 511", "CTA 1 thread 0", "CTA 1 thread 511"]):
         print(who + ": " + ", ".join(f"{names[e]} {buf[i, e] - buf[i, 0]}" for e in range(1, 8)))
+        chunks = [f"chunk {c}: weights landed {buf[i, 8 + 2 * c] - buf[i, 0]}, multiplied {buf[i, 9 + 2 * c] - buf[i, 0]}"
+                  for c in range(4) if buf[i, 8 + 2 * c]]
+        if chunks:
+            print("    " + "; ".join(chunks))
 
 
 def main(argv):
