@@ -301,7 +301,7 @@ print("variant ok")
 """
 
 
-@pytest.mark.parametrize("variant", ["121", "1121", "1141", "1221", "2", "22", "1"])
+@pytest.mark.parametrize("variant", ["121", "1121", "1141", "1221", "2", "22", "3", "1"])
 def test_every_kernel_variant_exact(variant):
     import os
     import subprocess
@@ -310,3 +310,48 @@ def test_every_kernel_variant_exact(variant):
     env = dict(os.environ, ONEBIT_PREFILL_VARIANT=variant)
     r = subprocess.run([sys.executable, "-c", _VARIANT_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "variant ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+# ---- the persistent CTA-pair kernel walking several output tiles per cluster --------------------------------
+
+_PERSISTENT_CHILD = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import oracle
+from onebitsparsemul_b200 import _lib
+from tests import helpers
+lib = _lib.load()
+rng = np.random.default_rng(11)
+# 10 row blocks x 9 token blocks = 90 tiles on 74 clusters; 3 weight tiles along k (an odd count: the last
+# pipeline stage is half full); the last token block is ragged
+m, n, k = 2560, 2296, 384
+dense, scale = helpers.make_weights(rng, m, k)
+canon, signs, _ = oracle.compress(dense)
+bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, 0)
+bt, mt = helpers.tile_order_from_canonical(canon, signs)
+B = helpers.make_tokens(rng, k, n, "int")
+want, _ = oracle.gemm(bits, meta, 0, B, m)
+t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+d_bt, d_mt, d_b = t(bt), t(mt), t(B)
+out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+_lib.check(lib.onebit_matmul_packed(d_bt.data_ptr(), d_mt.data_ptr(), None, d_b.data_ptr(), out.data_ptr(), m, n, k, _lib.OUT_F16, _lib.KERNEL_PREFILL, None))
+_lib.check(lib.onebit_check_device_status())
+assert (out.cpu().numpy() == want.astype(np.float16)).all(), "reference layout"
+x = d_b.t().contiguous()
+y = torch.full((n, m), float("nan"), dtype=torch.float16, device="cuda")
+_lib.check(lib.onebit_linear_tokens(d_bt.data_ptr(), d_mt.data_ptr(), None, None, x.data_ptr(), y.data_ptr(), m, n, k, _lib.OUT_F16, _lib.KERNEL_PREFILL, None))
+_lib.check(lib.onebit_check_device_status())
+assert (y.cpu().numpy() == want.astype(np.float16).T).all(), "token-major"
+print("persistent ok")
+"""
+
+
+def test_persistent_pair_kernel_many_tiles_exact():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ONEBIT_PREFILL_VARIANT="3")
+    r = subprocess.run([sys.executable, "-c", _PERSISTENT_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "persistent ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
