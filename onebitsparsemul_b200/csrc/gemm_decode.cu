@@ -174,6 +174,7 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
   // one token (n == 1) in the reference layout is the same contiguous vector as a token-major row
   const bool rows_contiguous = TM || a.n == 1;
+  const bool quad_rows = !rows_contiguous && (a.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 7) == 0);
   const bool vec_rows = !rows_contiguous && (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
 
   // 2. tokens of one round: at most two 16-byte pieces per thread, fetched into registers, then scattered
@@ -194,6 +195,11 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
         if ((kk >> 7) < ntile) {
           if (vec_rows) {
             tv[i] = __ldg(reinterpret_cast<const uint4*>(a.b + (k0 + kk) * a.n + n0 + pc * 8));
+          } else if (quad_rows) {
+            uint2* h4 = reinterpret_cast<uint2*>(&tv[i]);     // n % 4 == 0: whole groups of four tokens
+#pragma unroll
+            for (int q4 = 0; q4 < 2; ++q4)
+              if (8 * pc + 4 * q4 < nvalid) h4[q4] = __ldg(reinterpret_cast<const uint2*>(a.b + (k0 + kk) * a.n + n0 + 8 * pc + 4 * q4));
           } else {
             __half* h = reinterpret_cast<__half*>(&tv[i]);
 #pragma unroll

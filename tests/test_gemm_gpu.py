@@ -355,3 +355,49 @@ def test_persistent_pair_kernel_many_tiles_exact():
     env = dict(os.environ, ONEBIT_PREFILL_VARIANT="3")
     r = subprocess.run([sys.executable, "-c", _PERSISTENT_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "persistent ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+# ---- the decode kernel with slices longer than its shared-memory ring (weight slots refilled) ----------------
+
+_DECODE_RING_CHILD = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import oracle
+from onebitsparsemul_b200 import _lib
+from tests import helpers
+lib = _lib.load()
+rng = np.random.default_rng(13)
+m, k = 256, 128 * 37                        # one CTA per row block walks all 37 k tiles: 10 rounds of 4
+dense, scale = helpers.make_weights(rng, m, k)
+canon, signs, _ = oracle.compress(dense)
+bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, 0)
+bt, mt = helpers.tile_order_from_canonical(canon, signs)
+t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+d_bt, d_mt = t(bt), t(mt)
+for n in (1, 4, 5, 8, 12, 16):
+    B = helpers.make_tokens(rng, k, n, "int")
+    want, _ = oracle.gemm(bits, meta, 0, B, m)
+    d_b = t(B)
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(lib.onebit_matmul_packed(d_bt.data_ptr(), d_mt.data_ptr(), None, d_b.data_ptr(), out.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_DECODE, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want).all(), ("reference layout", n)
+    x = d_b.t().contiguous()
+    y = torch.full((n, m), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(lib.onebit_linear_tokens(d_bt.data_ptr(), d_mt.data_ptr(), None, None, x.data_ptr(), y.data_ptr(), m, n, k, _lib.OUT_F32, _lib.KERNEL_DECODE, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (y.cpu().numpy() == want.T).all(), ("token-major", n)
+print("decode ring ok")
+"""
+
+
+@pytest.mark.parametrize("split", ["1", "2"])
+def test_decode_kernel_long_slices_exact(split):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ONEBIT_DECODE_SPLIT=split)
+    r = subprocess.run([sys.executable, "-c", _DECODE_RING_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "decode ring ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
