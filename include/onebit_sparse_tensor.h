@@ -85,6 +85,17 @@ int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, in
 int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
+/* onebit_matmul_packed with fp16 output written to SEVERAL buffers in one pass: d (m, n) and n_extra <= 7
+ * more buffers of the same shape and row stride n, given as a HOST array of device-accessible pointers
+ * (16-byte aligned). Meant for a GEMM sharded by rows of A over the GPUs of one node whose full result
+ * every GPU needs: each GPU passes, as extra destinations, the addresses of its row slab inside the peers'
+ * copies of C (peer-mapped memory), and the epilogue's stores cross NVLink while the next tile is being
+ * multiplied -- the all-gather is fused into the GEMM. The caller orders the GPUs before and after
+ * (a barrier before peers may be overwritten, one before they are read). Needs m % 256 == 0, k % 128 == 0,
+ * n % 8 == 0. No counterpart in the reference, which is single-GPU (csrc/kernel_lib.cu:23-97). */
+int onebit_matmul_packed_scatter(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
+                                 void *const *extra_dst, int n_extra, int64_t m, int64_t n, int64_t k, void *stream);
+
 /* The same product in the nn.Linear convention, for callers that keep activations token-major:
  *   y (n, m) = x (n, k) @ W^T (+ bias),  x fp16 row-major, y fp16 / fp32 row-major, bias fp16 (m) or NULL,
  * W given by its tile-ordered operands and optional per-row scale. It is C^T = (A_sparse x B)^T with

@@ -19,7 +19,7 @@ __all__ = [
     "cuda_binary_mul", "cuda_binary_mul_", "binary_quant", "pack_binary", "unpack_binary", "dequant_desparse_tile",
     "py_binary_gemm", "BinaryLinear_2_4", "sparse_semi_structured_from_dense_cutlass",
     "sparse_semi_structured_to_dense_cutlass", "mask_creator", "PackedWeight", "pack_weight", "matmul_packed",
-    "relayout", "matmul_rows", "matmul_packed_host", "linear_tokens", "replace_linear_layers", "OneBitError",
+    "relayout", "matmul_rows", "matmul_scatter", "matmul_packed_host", "linear_tokens", "replace_linear_layers", "OneBitError",
 ]
 
 
@@ -265,6 +265,26 @@ def matmul_rows(pw: PackedWeight, B, out, row0: int, rows: int, kernel=KERNEL_AU
     with torch.cuda.device(B.device):
         _lib.check(lib.onebit_matmul_packed(pw.bits_tile.data_ptr() + tiles * 1024, pw.meta_tile.data_ptr() + tiles * 2048,
                                             scale_ptr, _ptr(B), _ptr(out), rows, n, pw.k, _out_code(out.dtype), kernel, _stream()))
+    return out
+
+
+def matmul_scatter(pw: PackedWeight, B, out, extra_ptrs):
+    """out (m, n) fp16 = pw @ B, written in the same pass to `out` and to every address in
+    `extra_ptrs` (at most 7 integers: device-accessible, 16-byte aligned buffers of out's shape, e.g. this
+    rank's row slab inside the peers' copies of C): ``onebit_matmul_packed_scatter``. The caller orders the
+    GPUs around the call."""
+    import ctypes
+    lib = _lib.load()
+    if not B.is_cuda or B.dtype != torch.float16 or B.shape[0] != pw.k:
+        raise ValueError("B must be a CUDA float16 tensor of shape (k, n)")
+    B = B.contiguous()
+    n = B.shape[1]
+    if tuple(out.shape) != (pw.m, n) or out.dtype != torch.float16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous float16 (m, n) tensor")
+    extra = (ctypes.c_void_p * max(1, len(extra_ptrs)))(*[int(p) for p in extra_ptrs])
+    with torch.cuda.device(B.device):
+        _lib.check(lib.onebit_matmul_packed_scatter(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(B), _ptr(out),
+                                                    ctypes.cast(extra, ctypes.c_void_p), len(extra_ptrs), pw.m, n, pw.k, _stream()))
     return out
 
 

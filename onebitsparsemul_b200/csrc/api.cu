@@ -16,9 +16,10 @@
 #include "formats.h"
 #include "kernels.h"
 
-static_assert(ONEBIT_META_PYTHON == OB_META_PYTHON && ONEBIT_META_CUTLASS == OB_META_CUTLASS, "enum drift");
-static_assert(ONEBIT_OUT_F32 == OB_OUT_F32 && ONEBIT_OUT_F16 == OB_OUT_F16, "enum drift");
-static_assert(ONEBIT_DENSE_F16 == OB_DENSE_F16 && ONEBIT_DENSE_BF16 == OB_DENSE_BF16 && ONEBIT_DENSE_I32 == OB_DENSE_I32, "enum drift");
+static_assert((int)ONEBIT_META_PYTHON == (int)OB_META_PYTHON && (int)ONEBIT_META_CUTLASS == (int)OB_META_CUTLASS, "enum drift");
+static_assert((int)ONEBIT_OUT_F32 == (int)OB_OUT_F32 && (int)ONEBIT_OUT_F16 == (int)OB_OUT_F16, "enum drift");
+static_assert((int)ONEBIT_DENSE_F16 == (int)OB_DENSE_F16 && (int)ONEBIT_DENSE_BF16 == (int)OB_DENSE_BF16 && (int)ONEBIT_DENSE_I32 == (int)OB_DENSE_I32,
+              "enum drift");
 
 namespace {
 
@@ -183,6 +184,26 @@ int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const voi
     return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
   }
   return ONEBIT_OK;
+}
+
+int onebit_matmul_packed_scatter(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
+                                 void* const* extra_dst, int n_extra, int64_t m, int64_t n, int64_t k, void* stream) {
+  if (!bits_tile || !meta_tile || !b || !d) return fail(ONEBIT_ERR_NULL, "null operand pointer");
+  if (n_extra < 0 || n_extra > 7) return fail(ONEBIT_ERR_ARG, "n_extra = %d, at most 7 extra destinations", n_extra);
+  if (n_extra > 0 && !extra_dst) return fail(ONEBIT_ERR_NULL, "null destination list");
+  for (int e = 0; e < n_extra; ++e) {
+    if (!extra_dst[e]) return fail(ONEBIT_ERR_NULL, "null extra destination %d", e);
+    if (reinterpret_cast<uintptr_t>(extra_dst[e]) & 15) return fail(ONEBIT_ERR_ARG, "extra destination %d is not 16-byte aligned", e);
+  }
+  if (!ob::prefill_scatter_supported(m, n, k, d))
+    return fail(ONEBIT_ERR_SHAPE,
+                "the multi-destination GEMM needs m %% 256 == 0, k %% 128 == 0, n %% 8 == 0 and a 16-byte aligned d "
+                "(got m=%lld n=%lld k=%lld)", (long long)m, (long long)n, (long long)k);
+  int* status = nullptr;
+  if (int rc = get_status_word(&status)) return rc;
+  cudaError_t e = ob::launch_gemm_prefill_scatter(bits_tile, meta_tile, scale, b, d, extra_dst, n_extra, m, n, k, status,
+                                                  static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "multi-destination GEMM launch");
 }
 
 int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const void* e_meta, const void* scale, int64_t m,

@@ -28,6 +28,15 @@ namespace {
 
 using namespace ob_ptx;
 
+// Timeline instrumentation for tuning, compiled in only with -DOB_TRACE: the two CTAs of one cluster record
+// the SM clock per output tile (events 0-7 leader, 8-15 partner).
+#ifdef OB_TRACE
+__device__ long long g_trace3[16][512];
+#define OB_TRACE_EV(ev, it) do { if ((blockIdx.x >> 1) == 5 && (it) < 512) g_trace3[(ev) + 8 * (blockIdx.x & 1)][it] = clock64(); } while (0)
+#else
+#define OB_TRACE_EV(ev, it) do { } while (0)
+#endif
+
 constexpr int BM = 128;              // weight rows per CTA
 constexpr int BK = 128;              // dense k per weight tile
 constexpr int BN = 256;              // tokens per CTA pair
@@ -43,7 +52,8 @@ struct Cfg3 {
   static constexpr int kECols = KS * 8;
   static constexpr int kASlotCols = KS * 32;
   static constexpr int kTmemCols = 512;            // 256 + 16 + 192 used
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512;
+  static constexpr int kEpiBytes = 4 * 2048;       // per epilogue warp: 32 rows x 64 bytes of output in flight
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kEpiBytes;
   static constexpr int kThreads = 32 * (2 + 4 + 4);   // producer, MMA, 4 expander warps, 4 epilogue warps
   static_assert(kSmemBytes <= 227 * 1024, "stages exceed shared memory");
   static_assert(kAccCols + kECols + kStages * kASlotCols <= 512, "tensor memory exceeded");
@@ -54,7 +64,8 @@ struct Prefill3Args {
   const uint8_t* meta_tile;
   const __half* scale;
   const __half* bias;      // per output row, added after the scale (NULL = none)
-  __half* d;
+  __half* d[8];           // reference layout: every destination receives the whole result (d[0] = the caller's C)
+  int n_dst;
   int64_t m, n, k;
   int row_blocks;          // m / 256
   int total_tiles;         // row_blocks * ceil(n / 256)
@@ -80,6 +91,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
   const uint32_t bar_acc_full = bar_base + 8 * (3 * C::kStages);                 // a tile's MMAs are done
   const uint32_t bar_acc_empty = bar_acc_full + 8;                               // leader only: both CTAs drained the accumulator
   const uint32_t tmem_slot = bar_acc_empty + 8;
+  const uint32_t epi_buf = bar_base + 512;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,6 +136,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
   };
   const int npre = min(C::kStages, total_its);
 
+  if (threadIdx.x == 0) OB_TRACE_EV(7, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); mbar_init(bar_afull(s), 2 * 4); }
     mbar_init(bar_acc_full, 1);
@@ -159,6 +172,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
       for (int tl = 0; tl < my_tiles; ++tl) {
         // the accumulator of the previous tile must have been drained by both CTAs' epilogues
         if (tl > 0) { mbar_wait(bar_acc_empty, (tl - 1) & 1, budget, a.status, 7); tcgen05_fence_after(); }
+        OB_TRACE_EV(0, tl);
         for (int it = 0; it < nit; ++it, ++gi) {
           const int s = gi % C::kStages;
           const int tiles = min(KS, kt - it * KS);
@@ -182,6 +196,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
           tcgen05_commit_2cta(bar_empty(s), 3);                // frees stage s and operand slot s in both CTAs
         }
         tcgen05_commit_2cta(bar_acc_full, 3);
+        OB_TRACE_EV(1, tl);
       }
     }
   } else if (warp < 6) {
@@ -220,6 +235,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
       const bool has_bias = a.bias != nullptr;
       const float bs = has_bias ? __half2float(a.bias[row]) : 0.f;
       mbar_wait(bar_acc_full, tl & 1, budget, a.status, 5);
+      if (q == 0 && lane == 0) OB_TRACE_EV(2, tl);
       tcgen05_fence_after();
       // drain: the whole accumulator row as packed fp16 in registers
       uint32_t h[BN / 2];
@@ -239,24 +255,57 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_acc_empty, 0));
+      if (q == 0 && lane == 0) OB_TRACE_EV(3, tl);
       // stores, overlapped with the next tile's main loop
       if constexpr (TM) {
 #pragma unroll
         for (int j = 0; j < BN / 2; ++j) {
           const int64_t t0 = nbase + 2 * j;
           const __half2 p = *reinterpret_cast<const __half2*>(&h[j]);
-          if (t0 < a.n) a.d[t0 * a.m + row] = __low2half(p);
-          if (t0 + 1 < a.n) a.d[(t0 + 1) * a.m + row] = __high2half(p);
+          if (t0 < a.n) a.d[0][t0 * a.m + row] = __low2half(p);
+          if (t0 + 1 < a.n) a.d[0][(t0 + 1) * a.m + row] = __high2half(p);
         }
-      } else {
-        __half* dst = a.d + row * a.n + nbase;
+      } else if (a.n_dst == 1) {
+        // Reference layout, one destination: 16-byte stores straight from the registers (a thread owns a
+        // row). Nothing here touches shared memory, whose port the main loop saturates: a staged epilogue
+        // took 13 000 cycles per tile, which a short k loop cannot hide.
+        __half* dst = a.d[0] + row * a.n + nbase;
 #pragma unroll
         for (int j = 0; j < BN / 8; ++j)
           if (nbase + 8 * j < a.n) *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+      } else {
+        // Reference layout, several destinations (C itself and, for a row-sharded GEMM whose result every
+        // GPU needs, the same rows of the peers' C over NVLink). 16-byte pieces of 32 different rows per
+        // instruction would waste the link, so the warp passes 32 tokens at a time through its own 2 KiB
+        // of shared memory (XOR-swizzled, conflict-free both ways) and writes 8 rows x 64 bytes per
+        // instruction to every destination.
+        uint8_t* wbuf = smem_gen + (epi_buf - smem_base) + q * 2048;
+        const int64_t row_base = ((int64_t)pb * 2 + cta) * BM + q * 32;
+#pragma unroll
+        for (int gch = 0; gch < BN / 32; ++gch) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(wbuf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                make_uint4(h[16 * gch + 4 * c], h[16 * gch + 4 * c + 1], h[16 * gch + 4 * c + 2], h[16 * gch + 4 * c + 3]);
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = (lane >> 2) + 8 * i, ch = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(wbuf + r * 64 + ((ch ^ ((r >> 1) & 3)) << 4));
+            const int64_t col = nbase + gch * 32 + ch * 8;
+            if (col < a.n) {
+              const int64_t off = (row_base + r) * a.n + col;
+              for (int e = 0; e < a.n_dst; ++e) *reinterpret_cast<uint4*>(a.d[e] + off) = v;
+            }
+          }
+          __syncwarp();
+        }
       }
+      if (q == 0 && lane == 0) OB_TRACE_EV(4, tl);
     }
   }
 
+  if (threadIdx.x == 0) OB_TRACE_EV(7, 1);
   __syncthreads();
   cluster_sync_all();               // the partner may still signal this CTA's barriers or read its memory
   if (warp == 1) {
@@ -301,7 +350,9 @@ cudaError_t launch3(const CUtensorMap& tmap, const Prefill3Args& a, cudaStream_t
 namespace ob {
 
 // fp16 output only (the drained tile lives in registers as packed fp16); d must be 16-byte aligned in
-// the reference layout. tmap as for launch_gemm_prefill2 with two weight tiles per stage.
+// the reference layout. tmap as for launch_gemm_prefill2 with two weight tiles per stage. extra_dst: up to
+// 7 more buffers of the shape of d (reference layout only) that receive the same result, e.g. the peers'
+// copies of C in a row-sharded GEMM.
 bool prefill3_supported(int64_t m, int64_t n, int64_t k, int out_type, const void* d, bool token_major) {
   return m % (2 * BM) == 0 && k % BK == 0 && k >= BK && n >= 1 && out_type == OB_OUT_F16 &&
          (token_major || (n % 8 == 0 && (reinterpret_cast<uintptr_t>(d) & 15) == 0)) &&
@@ -309,12 +360,31 @@ bool prefill3_supported(int64_t m, int64_t n, int64_t k, int out_type, const voi
 }
 
 cudaError_t launch_gemm_prefill3(const CUtensorMap* tmap, bool token_major, const void* bits_tile, const void* meta_tile,
-                                 const void* scale, const void* bias, void* d, int64_t m, int64_t n, int64_t k, int* status,
-                                 cudaStream_t stream) {
-  Prefill3Args a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-                 static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<__half*>(d), m, n, k,
-                 (int)(m / (2 * BM)), (int)((m / (2 * BM)) * ((n + BN - 1) / BN)), status};
+                                 const void* scale, const void* bias, void* d, void* const* extra_dst, int n_extra,
+                                 int64_t m, int64_t n, int64_t k, int* status, cudaStream_t stream) {
+  if (n_extra < 0 || n_extra > 7 || (n_extra > 0 && token_major)) return cudaErrorInvalidValue;
+  Prefill3Args a{};
+  a.bits_tile = static_cast<const uint8_t*>(bits_tile);
+  a.meta_tile = static_cast<const uint8_t*>(meta_tile);
+  a.scale = static_cast<const __half*>(scale);
+  a.bias = static_cast<const __half*>(bias);
+  a.d[0] = static_cast<__half*>(d);
+  for (int e = 0; e < n_extra; ++e) {
+    if ((reinterpret_cast<uintptr_t>(extra_dst[e]) & 15) != 0) return cudaErrorMisalignedAddress;
+    a.d[1 + e] = static_cast<__half*>(extra_dst[e]);
+  }
+  a.n_dst = 1 + n_extra;
+  a.m = m; a.n = n; a.k = k;
+  a.row_blocks = (int)(m / (2 * BM));
+  a.total_tiles = (int)((m / (2 * BM)) * ((n + BN - 1) / BN));
+  a.status = status;
   return token_major ? launch3<true>(*tmap, a, stream) : launch3<false>(*tmap, a, stream);
 }
 
 }  // namespace ob
+
+#ifdef OB_TRACE
+extern "C" int onebit_debug_read_trace3(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace3, sizeof(long long) * 16 * 512);
+}
+#endif

@@ -329,8 +329,8 @@ cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tma
                                  cudaStream_t stream);
 bool prefill3_supported(int64_t m, int64_t n, int64_t k, int out_type, const void* d, bool token_major);
 cudaError_t launch_gemm_prefill3(const CUtensorMap* tmap, bool token_major, const void* bits_tile, const void* meta_tile,
-                                 const void* scale, const void* bias, void* d, int64_t m, int64_t n, int64_t k, int* status,
-                                 cudaStream_t stream);
+                                 const void* scale, const void* bias, void* d, void* const* extra_dst, int n_extra,
+                                 int64_t m, int64_t n, int64_t k, int* status, cudaStream_t stream);
 
 namespace {
 int forced_variant() {
@@ -376,7 +376,7 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   if ((forced == 3 || (forced == 0 && pair_fits && k <= 4096)) && prefill3_supported(m, n, k, out_type, d, false)) {
     CUtensorMap tmap3;
     if (!make_map(&tmap3, BK * 2)) return cudaErrorInvalidValue;
-    return launch_gemm_prefill3(&tmap3, false, bits_tile, meta_tile, scale, nullptr, d, m, n, k, status, stream);
+    return launch_gemm_prefill3(&tmap3, false, bits_tile, meta_tile, scale, nullptr, d, nullptr, 0, m, n, k, status, stream);
   }
   if (((forced == 2 || forced == 22) && prefill2_supported(m, n, k)) || (forced == 0 && pair_fits)) {
     const int ks = (forced == 2) ? 1 : 2;
@@ -414,6 +414,29 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   return launch<1, 128, 1, true>(tmap, a, stream);
 }
 
+// The persistent pair kernel writing the fp16 result to C and to n_extra more buffers of C's shape.
+bool prefill_scatter_supported(int64_t m, int64_t n, int64_t k, const void* d) {
+  return prefill3_supported(m, n, k, OB_OUT_F16, d, false);
+}
+
+cudaError_t launch_gemm_prefill_scatter(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                                        void* d, void* const* extra_dst, int n_extra, int64_t m, int64_t n, int64_t k,
+                                        int* status, cudaStream_t stream) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(b) & 15) != 0) return cudaErrorMisalignedAddress;
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)k};
+  const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)(2 * BK)};
+  const cuuint32_t estr[2] = {1, 1};
+  if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  return launch_gemm_prefill3(&tmap, false, bits_tile, meta_tile, scale, nullptr, d, extra_dst, n_extra, m, n, k, status, stream);
+}
+
 bool prefill_tokens_supported(int64_t m, int64_t n, int64_t k) { return prefill2_supported(m, 8, k) && n >= 1; }
 
 // Token-major form (the nn.Linear convention): x (n, k) row-major fp16, y (n, m) row-major, optional
@@ -437,7 +460,7 @@ cudaError_t launch_gemm_prefill_tokens(const void* bits_tile, const void* meta_t
       return cudaErrorInvalidValue;
   }
   if (forced_variant() == 3 && prefill3_supported(m, n, k, out_type, y, true))
-    return launch_gemm_prefill3(&tmap_x, true, bits_tile, meta_tile, scale, bias, y, m, n, k, status, stream);
+    return launch_gemm_prefill3(&tmap_x, true, bits_tile, meta_tile, scale, bias, y, nullptr, 0, m, n, k, status, stream);
   bool y_map = false;
   if (out_type == OB_OUT_F16 && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
     const cuuint64_t dims[2] = {(cuuint64_t)m, (cuuint64_t)n};

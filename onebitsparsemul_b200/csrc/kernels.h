@@ -37,6 +37,12 @@ cudaError_t launch_gemm_prefill_tokens(const void* bits_tile, const void* meta_t
                                        const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type, int* status,
                                        cudaStream_t stream);
 bool prefill_tokens_supported(int64_t m, int64_t n, int64_t k);
+// K2 persistent pair kernel with several destinations: the fp16 result goes to d and to n_extra (<= 7) more
+// buffers of the same shape (any address this device can store to, e.g. peer GPUs' memory).
+cudaError_t launch_gemm_prefill_scatter(const void* bits_tile, const void* meta_tile, const void* scale, const void* b,
+                                        void* d, void* const* extra_dst, int n_extra, int64_t m, int64_t n, int64_t k,
+                                        int* status, cudaStream_t stream);
+bool prefill_scatter_supported(int64_t m, int64_t n, int64_t k, const void* d);
 cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
                                       cudaStream_t stream);

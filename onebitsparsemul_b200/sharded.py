@@ -11,6 +11,13 @@ only when the caller asks for the full C on every rank:
   gather="all"      one NCCL all-gather after the GEMM
   gather="overlap"  the slab is computed in row chunks; chunk c travels (grouped send/recv into the
                     right rows of the full C) on a side stream while chunk c+1 is computed
+  gather="fused"    no collective kernel at all: the GEMM's epilogue stores every output tile into this
+                    rank's C and, through peer-mapped memory, into the same rows of every other rank's C
+                    while the next tile is multiplied (``onebit_matmul_packed_scatter``). C lives in a
+                    buffer all ranks have mapped (symmetric memory, else CUDA IPC handles); two tiny
+                    all-reduces order the ranks before peers are overwritten and before C is read.
+                    The returned tensor is that cached buffer: the next fused call of the same shape
+                    overwrites it.
 
 One process per GPU, ``torch.distributed`` for the plumbing. Slabs are whole 256-row blocks so that
 every rank runs the same kernel variants as a single GPU would; results are bit-identical to the
@@ -57,7 +64,7 @@ class ShardedBinaryLinear:
     """
 
     def __init__(self, outfeatures: int, infeatures: int, group: Optional[dist.ProcessGroup] = None,
-                 matmul: Optional[Callable] = None, pack: Optional[Callable] = None):
+                 matmul: Optional[Callable] = None, pack: Optional[Callable] = None, scatter: Optional[Callable] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -67,6 +74,10 @@ class ShardedBinaryLinear:
         self._matmul, self._pack = matmul, pack
         self.packed = None
         self._side = None
+        self._scatter = scatter
+        self._fused = {}                 # n -> (full C, peers' base addresses, keep-alive objects)
+        self._flag = None
+        self.fused_backend = None        # "symmetric_memory" or "ipc", once a fused buffer exists
 
     # -- weights ---------------------------------------------------------------------------------------
     def pack_slab(self, weight_slab, scale_slab=None, apply_mask=True):
@@ -100,6 +111,8 @@ class ShardedBinaryLinear:
             out = torch.empty((self.rows, n), dtype=out_dtype, device=dev)
             self._gemm(B, out)
             return out
+        if gather == "fused":
+            return self._forward_fused(B, out_dtype)
         full = torch.empty((self.m, n), dtype=out_dtype, device=dev)
         mine = full[self.start:self.start + self.rows]
         if gather == "all" and len({r for _, r in self.partition}) == 1:
@@ -139,4 +152,59 @@ class ShardedBinaryLinear:
             w.wait()
         if cuda:
             torch.cuda.current_stream().wait_stream(self._side)
+        return full
+
+    # -- fused GEMM + all-gather ------------------------------------------------------------------------
+    def _peer_mapped_buffer(self, n, dev):
+        """A (m, n) fp16 buffer on every rank that all ranks can store to: returns (tensor, [base address
+        of rank p's buffer as seen from this process], keep-alive)."""
+        shape = (self.m, n)
+        try:
+            import torch.distributed._symmetric_memory as symm
+            group = self.group if self.group is not None else dist.group.WORLD
+            full = symm.empty(shape, dtype=torch.float16, device=dev)
+            handle = symm.rendezvous(full, group)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            self.fused_backend = "symmetric_memory"
+            return full, ptrs, handle
+        except Exception:                                # fall back to plain CUDA IPC handles
+            full = torch.empty(shape, dtype=torch.float16, device=dev)
+            mine = full.untyped_storage()._share_cuda_()
+            handles = [None] * self.world
+            dist.all_gather_object(handles, (mine, full.storage_offset() * 2), group=self.group)
+            ptrs, keep = [], []
+            for p, (h, off) in enumerate(handles):
+                if p == self.rank:
+                    ptrs.append(full.data_ptr())
+                    continue
+                st = torch.UntypedStorage._new_shared_cuda(*h)
+                peer = torch.empty(0, dtype=torch.float16, device=st.device).set_(st, off // 2, shape)
+                peer[:1, :1].to(dev)                     # a first copy makes torch enable peer access dev -> peer
+                ptrs.append(peer.data_ptr())
+                keep.append((st, peer))
+            self.fused_backend = "ipc"
+            return full, ptrs, keep
+
+    def _rank_barrier(self, dev):
+        """Stream-ordered barrier: no rank's later work starts before every rank's earlier work is done."""
+        if self._flag is None:
+            self._flag = torch.zeros(1, dtype=torch.float32, device=dev)
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _forward_fused(self, B, out_dtype):
+        if out_dtype != torch.float16:
+            raise ValueError("gather='fused' produces float16")
+        n, dev = B.shape[1], B.device
+        if n not in self._fused:
+            self._fused[n] = self._peer_mapped_buffer(n, dev)
+        full, ptrs, _ = self._fused[n]
+        mine = full[self.start:self.start + self.rows]
+        extra = [ptrs[p] + self.start * n * 2 for p in range(self.world) if p != self.rank]
+        self._rank_barrier(dev)                          # every rank is done reading the previous result
+        if self._scatter is not None:
+            self._scatter(self.packed, B, mine, extra)
+        else:
+            from . import matmul_scatter
+            matmul_scatter(self.packed, B, mine, extra)
+        self._rank_barrier(dev)                          # every rank's stores have landed
         return full

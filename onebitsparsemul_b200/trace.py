@@ -60,6 +60,21 @@ def trace_prefill(m, n, k):
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = [ctypes.c_void_p], ctypes.c_int
         fn(buf.ctypes.data)
+    pers = np.zeros((16, 512), np.int64)
+    fn = lib.onebit_debug_read_trace3
+    fn.argtypes, fn.restype = [ctypes.c_void_p], ctypes.c_int
+    fn(pers.ctypes.data)
+    if pers[7, 0] != 0:                                    # the persistent CTA-pair kernel ran
+        for c in (0, 1):
+            b = pers[8 * c:8 * c + 8]
+            t0 = b[7, 0]
+            print(f"CTA {c} of the traced cluster: kernel end {b[7, 1] - t0}")
+            print("  tile  MMA:accumulator free  MMA:tile committed  epilogue:accumulator full  epilogue:drained  epilogue:stored")
+            for tl in range(16):
+                if b[2, tl] == 0:
+                    break
+                print(f"  {tl:4d} " + "  ".join(f"{(b[e, tl] - t0) if b[e, tl] else 0:20d}" for e in (0, 1, 2, 3, 4)))
+        return
     if pair[7, 2] != 0:                                    # the CTA-pair kernel ran
         for c in (0, 1):
             b = pair[8 * c:8 * c + 8]

@@ -401,3 +401,22 @@ def test_decode_kernel_long_slices_exact(split):
     env = dict(os.environ, ONEBIT_DECODE_SPLIT=split)
     r = subprocess.run([sys.executable, "-c", _DECODE_RING_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "decode ring ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+# ---- one GEMM, several destinations (the fused all-gather's epilogue, here with local buffers) ---------------
+
+@pytest.mark.parametrize("m,n,k,n_extra", [(512, 264, 384, 1), (2560, 2296, 256, 3), (256, 8, 128, 7)])
+def test_scatter_epilogue_writes_every_destination(m, n, k, n_extra):
+    import onebitsparsemul_b200 as ob
+    rng = np.random.default_rng(17)
+    dense, scale = helpers.make_weights(rng, m, k)
+    pw = ob.pack_weight(torch.from_numpy(dense).cuda(), scale=torch.from_numpy(scale).cuda())
+    B = torch.from_numpy(helpers.make_tokens(rng, k, n)).cuda()
+    want = ob.matmul_packed(pw, B, out_dtype=torch.float16, kernel=_lib.KERNEL_PREFILL)
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    extra = [torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda") for _ in range(n_extra)]
+    ob.matmul_scatter(pw, B, out, [e.data_ptr() for e in extra])
+    _lib.check(_lib.load().onebit_check_device_status())
+    assert torch.equal(out, want)
+    for e in extra:
+        assert torch.equal(e, want)

@@ -122,14 +122,18 @@ def _gpu_worker(rank, world, port, q):
         w, sc = torch.from_numpy(dense).cuda(), torch.from_numpy(scale).cuda()
         single = ob.pack_weight(w, scale=sc)
         layer = ShardedBinaryLinear(m, k).pack_full(w, sc)
-        ok = True
+        ok = []                                           # the (n, mode) cases that differ
         for n in (8, 512):
-            B = torch.from_numpy(helpers.make_tokens(rng, k, n)).cuda()
+            # integer tokens: every kernel variant gives the exact result, whatever its summation order
+            B = torch.from_numpy(helpers.make_tokens(rng, k, n, "int")).cuda()
             want = ob.matmul_packed(single, B, out_dtype=torch.float16)
             slab = layer.forward(B, gather="none")
-            ok &= bool((slab == want[layer.start:layer.start + layer.rows]).all())
-            for mode in ("all", "overlap"):
-                ok &= bool((layer.forward(B, gather=mode) == want).all())
+            if not bool((slab == want[layer.start:layer.start + layer.rows]).all()):
+                ok.append((n, "none"))
+            for mode in ("all", "overlap", "fused", "fused"):     # fused twice: the cached peer-mapped buffer is reused
+                if not bool((layer.forward(B, gather=mode) == want).all()):
+                    ok.append((n, mode))
+        ok = (ok == [], ok, layer.fused_backend)
         torch.cuda.synchronize()
         q.put((rank, ok))
     finally:
@@ -148,7 +152,7 @@ def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
         layer = ShardedBinaryLinear(512, 256).pack_full(w)
         B = torch.from_numpy(helpers.make_tokens(rng, 256, 32)).cuda()
         want = ob.matmul_packed(ob.pack_weight(w), B, out_dtype=torch.float16)
-        for mode in ("none", "all", "overlap"):
+        for mode in ("none", "all", "overlap", "fused"):
             assert (layer.forward(B, gather=mode) == want).all()
         return
     ctx = mp.get_context("spawn")
@@ -161,4 +165,4 @@ def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    assert all(ok for _, ok in results), results
+    assert all(ok[0] for _, ok in results), results
