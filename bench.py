@@ -365,7 +365,7 @@ def run_sharded(args):
                           "scaling": "strong", "dtype": "f16", "data": "synthetic",
                           "config": {"workload": f"ONE square GEMM {S}^3 row-sharded over {world} GPU(s), B replicated, "
                                                  f"gather={args.gather}", "rows_per_rank": layer.rows,
-                                     "out_shape": list(out.shape)}}), flush=True)
+                                     "out_shape": list(out.shape), "fused_backend": layer.fused_backend}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
