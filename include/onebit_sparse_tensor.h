@@ -81,7 +81,12 @@ int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, in
                     void *bits_tile, void *meta_tile, void *stream);
 
 /* GEMM on tile-ordered operands (the fast path; the hot loop of BinaryLinear_2_4.forward,
- * onebit_sparse_mul/__init__.py:118-128). kernel: ONEBIT_KERNEL_*. */
+ * onebit_sparse_mul/__init__.py:118-128). kernel: ONEBIT_KERNEL_*.
+ * The few-token kernel is launched with programmatic stream serialisation: its grid may start while the
+ * kernel before it in `stream` drains, and it requests the packed weights before it waits for that kernel
+ * (tokens are read, and d is written, only afterwards). Kernels of this library hand over early only after
+ * their own weight requests are out and never produce packed weights; any other kernel hands over when it
+ * has completed. Set ONEBIT_PDL=0 in the environment to launch it as an ordinary kernel. */
 int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
