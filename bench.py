@@ -47,26 +47,58 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs: NVML every 2 ms (the timed region
+    of a default run is tens of milliseconds), nvidia-smi as the fallback."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # NVML clocks-event-reason bits
+    REASON_BITS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, index):
-        self.index, self.samples, self.stop = index, [], threading.Event()
+    def __init__(self, index, uuid=None):
+        self.index, self.samples, self.stop = index, [], threading.Event()     # samples: (mhz, max mhz, reason bits)
+        self.handle = self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+        except Exception:
+            self.handle = None
         self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def sample_nvml(self):
+        n, h = self.nvml, self.handle
+        mhz = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        top = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(h)
+        except Exception:
+            bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        self.samples.append((int(mhz), int(top), int(bits)))
+
+    def sample_smi(self):
+        out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                              "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+        parts = [x.strip() for x in out.strip().split(",")]
+        if len(parts) >= 6 and parts[0].isdigit() and parts[1].isdigit():
+            order = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            bits = sum(dict(self.REASON_BITS)[name] for i, name in enumerate(order) if parts[2 + i].lower().startswith("active"))
+            self.samples.append((int(parts[0]), int(parts[1]), bits))
 
     def run(self):
         while not self.stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                parts = [x.strip() for x in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
+                if self.handle is not None:
+                    self.sample_nvml()
+                else:
+                    self.sample_smi()
             except Exception:
                 pass
-            self.stop.wait(0.02)
+            self.stop.wait(0.002 if self.handle is not None else 0.02)
 
     def __enter__(self):
         self.thread.start()
@@ -79,12 +111,13 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
-                "sm_max_mhz": int(self.samples[0][1]) if self.samples[0][1].isdigit() else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        mhz = sorted(s[0] for s in self.samples)
+        bits = 0
+        for s in self.samples:
+            bits |= s[2]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_min_mhz": mhz[0], "sm_max_mhz": self.samples[0][1],
+                "reasons": [name for name, bit in self.REASON_BITS if bits & bit], "samples": len(self.samples),
+                "source": "nvml" if self.handle is not None else "nvidia-smi"}
 
 
 def cpu_sample(size, rows, threads=0):
@@ -227,7 +260,11 @@ def run_ours(args):
 
     sync_all()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    with ClockSampler(local) as clocks:
+    try:
+        gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)    # NVML may number the GPUs differently
+    except Exception:
+        gpu_uuid = None
+    with ClockSampler(local, gpu_uuid) as clocks:
         ev[0].record()
         for i in range(args.steps):
             step()
