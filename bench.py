@@ -418,7 +418,7 @@ def main():
     ap.add_argument("--workload", default="square", choices=["square", "sharded"],
                     help="square: one size^3 GEMM per GPU (weak scaling, the contract's line); sharded: ONE size^3 GEMM "
                          "row-sharded over all ranks (strong scaling, supplementary)")
-    ap.add_argument("--gather", default="none", choices=["none", "all", "overlap", "fused"],
+    ap.add_argument("--gather", default="none", choices=["none", "all", "overlap", "fused", "push"],
                     help="sharded workload only: gather the full C on every rank")
     args = ap.parse_args()
     if args.impl == "reference":

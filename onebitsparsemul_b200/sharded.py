@@ -11,6 +11,10 @@ only when the caller asks for the full C on every rank:
   gather="all"      one NCCL all-gather after the GEMM
   gather="overlap"  the slab is computed in row chunks; chunk c travels (grouped send/recv into the
                     right rows of the full C) on a side stream while chunk c+1 is computed
+  gather="push"     the slab is computed in row chunks; as soon as a chunk is done, the copy engines push it
+                    into the same rows of every other rank's C (plain device-to-device copies to peer-mapped
+                    memory, one side stream per peer) while the next chunk is multiplied. No SM is spent on
+                    communication. Same cached peer-mapped C and rank ordering as "fused".
   gather="fused"    no collective kernel at all: the GEMM's epilogue stores every output tile into this
                     rank's C and, through peer-mapped memory, into the same rows of every other rank's C
                     while the next tile is multiplied (``onebit_matmul_packed_scatter``). C lives in a
@@ -78,6 +82,7 @@ class ShardedBinaryLinear:
         self._fused = {}                 # n -> (full C, peers' base addresses, keep-alive objects)
         self._flag = None
         self.fused_backend = None        # "symmetric_memory" or "ipc", once a fused buffer exists
+        self._push_streams = None
 
     # -- weights ---------------------------------------------------------------------------------------
     def pack_slab(self, weight_slab, scale_slab=None, apply_mask=True):
@@ -113,6 +118,8 @@ class ShardedBinaryLinear:
             return out
         if gather == "fused":
             return self._forward_fused(B, out_dtype)
+        if gather == "push":
+            return self._forward_push(B, out_dtype, chunks)
         full = torch.empty((self.m, n), dtype=out_dtype, device=dev)
         mine = full[self.start:self.start + self.rows]
         if gather == "all" and len({r for _, r in self.partition}) == 1:
@@ -157,7 +164,7 @@ class ShardedBinaryLinear:
     # -- fused GEMM + all-gather ------------------------------------------------------------------------
     def _peer_mapped_buffer(self, n, dev):
         """A (m, n) fp16 buffer on every rank that all ranks can store to: returns (tensor, [base address
-        of rank p's buffer as seen from this process], keep-alive)."""
+        of rank p's buffer as seen from this process], (handle, [tensor aliasing rank p's buffer]))."""
         shape = (self.m, n)
         try:
             import torch.distributed._symmetric_memory as symm
@@ -165,25 +172,27 @@ class ShardedBinaryLinear:
             full = symm.empty(shape, dtype=torch.float16, device=dev)
             handle = symm.rendezvous(full, group)
             ptrs = [int(p) for p in handle.buffer_ptrs]
+            views = [full if p == self.rank else handle.get_buffer(p, shape, torch.float16) for p in range(self.world)]
             self.fused_backend = "symmetric_memory"
-            return full, ptrs, handle
+            return full, ptrs, (handle, views)
         except Exception:                                # fall back to plain CUDA IPC handles
             full = torch.empty(shape, dtype=torch.float16, device=dev)
             mine = full.untyped_storage()._share_cuda_()
             handles = [None] * self.world
             dist.all_gather_object(handles, (mine, full.storage_offset() * 2), group=self.group)
-            ptrs, keep = [], []
+            ptrs, views = [], []
             for p, (h, off) in enumerate(handles):
                 if p == self.rank:
                     ptrs.append(full.data_ptr())
+                    views.append(full)
                     continue
                 st = torch.UntypedStorage._new_shared_cuda(*h)
                 peer = torch.empty(0, dtype=torch.float16, device=st.device).set_(st, off // 2, shape)
                 peer[:1, :1].to(dev)                     # a first copy makes torch enable peer access dev -> peer
                 ptrs.append(peer.data_ptr())
-                keep.append((st, peer))
+                views.append(peer)
             self.fused_backend = "ipc"
-            return full, ptrs, keep
+            return full, ptrs, (None, views)
 
     def _rank_barrier(self, dev):
         """Stream-ordered barrier: no rank's later work starts before every rank's earlier work is done."""
@@ -207,4 +216,31 @@ class ShardedBinaryLinear:
             from . import matmul_scatter
             matmul_scatter(self.packed, B, mine, extra)
         self._rank_barrier(dev)                          # every rank's stores have landed
+        return full
+
+    def _forward_push(self, B, out_dtype, chunks):
+        if out_dtype != torch.float16:
+            raise ValueError("gather='push' produces float16")
+        n, dev = B.shape[1], B.device
+        if n not in self._fused:
+            self._fused[n] = self._peer_mapped_buffer(n, dev)
+        full, _, (_, views) = self._fused[n]
+        mine = full[self.start:self.start + self.rows]
+        peers = [p for p in range(self.world) if p != self.rank]
+        if self._push_streams is None:
+            self._push_streams = [torch.cuda.Stream(device=dev) for _ in peers]
+        self._rank_barrier(dev)                          # every rank is done reading the previous result
+        main = torch.cuda.current_stream(dev)
+        for c0, crows in chunk_rows(self.rows, chunks):
+            self._gemm(B, mine[c0:c0 + crows], c0, crows)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            r0 = self.start + c0
+            for st, p in zip(self._push_streams, peers):
+                st.wait_event(ready)
+                with torch.cuda.stream(st):
+                    views[p][r0:r0 + crows].copy_(mine[c0:c0 + crows], non_blocking=True)
+        for st in self._push_streams:
+            main.wait_stream(st)
+        self._rank_barrier(dev)                          # every rank's copies have landed
         return full

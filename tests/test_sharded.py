@@ -130,7 +130,7 @@ def _gpu_worker(rank, world, port, q):
             slab = layer.forward(B, gather="none")
             if not bool((slab == want[layer.start:layer.start + layer.rows]).all()):
                 ok.append((n, "none"))
-            for mode in ("all", "overlap", "fused", "fused"):     # fused twice: the cached peer-mapped buffer is reused
+            for mode in ("all", "overlap", "fused", "fused", "push", "push"):   # twice: the cached peer-mapped buffer is reused
                 if not bool((layer.forward(B, gather=mode) == want).all()):
                     ok.append((n, mode))
         ok = (ok == [], ok, layer.fused_backend)
@@ -152,7 +152,7 @@ def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
         layer = ShardedBinaryLinear(512, 256).pack_full(w)
         B = torch.from_numpy(helpers.make_tokens(rng, 256, 32)).cuda()
         want = ob.matmul_packed(ob.pack_weight(w), B, out_dtype=torch.float16)
-        for mode in ("none", "all", "overlap", "fused"):
+        for mode in ("none", "all", "overlap", "fused", "push"):
             assert (layer.forward(B, gather=mode) == want).all()
         return
     ctx = mp.get_context("spawn")
