@@ -52,7 +52,7 @@ struct Cfg3 {
   static constexpr int kECols = KS * 8;
   static constexpr int kASlotCols = KS * 32;
   static constexpr int kTmemCols = 512;            // 256 + 16 + 192 used
-  static constexpr int kEpiBytes = 4 * 2048;       // per epilogue warp: 32 rows x 64 bytes of output in flight
+  static constexpr int kEpiBytes = 4 * 2048;       // per epilogue warp: 4 output rows (512 bytes each) in flight
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + kEpiBytes;
   static constexpr int kThreads = 32 * (2 + 4 + 4);   // producer, MMA, 4 expander warps, 4 epilogue warps
   static_assert(kSmemBytes <= 227 * 1024, "stages exceed shared memory");
@@ -73,7 +73,8 @@ struct Prefill3Args {
 };
 
 // TM = token-major operands (x (n, k), y (n, m)); false = the reference's B (k, n), C (m, n)
-template <bool TM>
+// MULTI = the result goes to a.n_dst > 1 buffers (reference layout only)
+template <bool TM, bool MULTI>
 __global__ void __launch_bounds__(Cfg3::kThreads, 1)
 ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args a) {
   using C = Cfg3;
@@ -265,7 +266,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
           if (t0 < a.n) a.d[0][t0 * a.m + row] = __low2half(p);
           if (t0 + 1 < a.n) a.d[0][(t0 + 1) * a.m + row] = __high2half(p);
         }
-      } else if (a.n_dst == 1) {
+      } else if constexpr (!MULTI) {
         // Reference layout, one destination: 16-byte stores straight from the registers (a thread owns a
         // row). Nothing here touches shared memory, whose port the main loop saturates: a staged epilogue
         // took 13 000 cycles per tile, which a short k loop cannot hide.
@@ -275,26 +276,30 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
           if (nbase + 8 * j < a.n) *reinterpret_cast<uint4*>(dst + 8 * j) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
       } else {
         // Reference layout, several destinations (C itself and, for a row-sharded GEMM whose result every
-        // GPU needs, the same rows of the peers' C over NVLink). 16-byte pieces of 32 different rows per
-        // instruction would waste the link, so the warp passes 32 tokens at a time through its own 2 KiB
-        // of shared memory (XOR-swizzled, conflict-free both ways) and writes 8 rows x 64 bytes per
-        // instruction to every destination.
+        // GPU needs, the same rows of the peers' C over NVLink). What crosses the link must be long
+        // contiguous runs: with 7 peer destinations, 16-byte pieces of 32 different rows per instruction
+        // took 10.3 ms for a 3328 x 25600 x 25600 slab, 64-byte segments 3.2 ms, whole 512-byte rows 2.4 ms
+        // (the GEMM alone: 1.5 ms). So the warp passes four of its rows at a time through its own 2 KiB of
+        // shared memory: the four owner lanes write their rows (16-byte chunks XOR-swizzled by the row, so
+        // the four lanes hit different banks), then every instruction stores one whole row, 32 lanes x 16
+        // bytes, to each destination.
         uint8_t* wbuf = smem_gen + (epi_buf - smem_base) + q * 2048;
         const int64_t row_base = ((int64_t)pb * 2 + cta) * BM + q * 32;
+#pragma unroll 1
+        for (int g4 = 0; g4 < 8; ++g4) {
+          if ((lane >> 2) == g4) {
+            uint8_t* myrow = wbuf + (lane & 3) * 512;
 #pragma unroll
-        for (int gch = 0; gch < BN / 32; ++gch) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(wbuf + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
-                make_uint4(h[16 * gch + 4 * c], h[16 * gch + 4 * c + 1], h[16 * gch + 4 * c + 2], h[16 * gch + 4 * c + 3]);
+            for (int j = 0; j < BN / 8; ++j)
+              *reinterpret_cast<uint4*>(myrow + ((j ^ (lane & 3)) << 4)) = make_uint4(h[4 * j], h[4 * j + 1], h[4 * j + 2], h[4 * j + 3]);
+          }
           __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = (lane >> 2) + 8 * i, ch = lane & 3;
-            const uint4 v = *reinterpret_cast<const uint4*>(wbuf + r * 64 + ((ch ^ ((r >> 1) & 3)) << 4));
-            const int64_t col = nbase + gch * 32 + ch * 8;
+          for (int ri = 0; ri < 4; ++ri) {
+            const uint4 v = *reinterpret_cast<const uint4*>(wbuf + ri * 512 + ((lane ^ ri) << 4));
+            const int64_t col = nbase + lane * 8;
             if (col < a.n) {
-              const int64_t off = (row_base + r) * a.n + col;
+              const int64_t off = (row_base + 4 * g4 + ri) * a.n + col;
               for (int e = 0; e < a.n_dst; ++e) *reinterpret_cast<uint4*>(a.d[e] + off) = v;
             }
           }
@@ -314,7 +319,7 @@ ob_gemm_prefill3_kernel(const __grid_constant__ CUtensorMap tmap_b, Prefill3Args
   }
 }
 
-template <bool TM>
+template <bool TM, bool MULTI>
 cudaError_t launch3(const CUtensorMap& tmap, const Prefill3Args& a, cudaStream_t stream) {
   using C = Cfg3;
   static bool configured[64] = {};
@@ -322,7 +327,7 @@ cudaError_t launch3(const CUtensorMap& tmap, const Prefill3Args& a, cudaStream_t
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill3_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill3_kernel<TM, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
@@ -342,7 +347,7 @@ cudaError_t launch3(const CUtensorMap& tmap, const Prefill3Args& a, cudaStream_t
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill3_kernel<TM>, tmap, a);
+  return cudaLaunchKernelEx(&cfg, ob_gemm_prefill3_kernel<TM, MULTI>, tmap, a);
 }
 
 }  // namespace
@@ -378,7 +383,8 @@ cudaError_t launch_gemm_prefill3(const CUtensorMap* tmap, bool token_major, cons
   a.row_blocks = (int)(m / (2 * BM));
   a.total_tiles = (int)((m / (2 * BM)) * ((n + BN - 1) / BN));
   a.status = status;
-  return token_major ? launch3<true>(*tmap, a, stream) : launch3<false>(*tmap, a, stream);
+  if (token_major) return launch3<true, false>(*tmap, a, stream);
+  return a.n_dst > 1 ? launch3<false, true>(*tmap, a, stream) : launch3<false, false>(*tmap, a, stream);
 }
 
 }  // namespace ob
