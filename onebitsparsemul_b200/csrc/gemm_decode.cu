@@ -11,10 +11,10 @@
 //     shared-memory ring. One thread issues the first ring right after initialising the mbarriers
 //     -- 36-48 KiB per CTA in flight before anything else happens -- and refills a slot once all
 //     8 warps have read it (longer slices only);
-//   * 8 warps = RS row sets x KL tile lanes: a warp multiplies RG 16-row groups (64 rows for n <= 8,
-//     32 rows for n <= 16) by ONE tile of the round, so that a token fragment read from shared
-//     memory feeds RG tensor-core instructions; with one row group per warp the kernel was bound by
-//     the shared-memory port, not by HBM;
+//   * 8 warps = 2 row sets x 4 tile lanes: a warp multiplies four 16-row groups (64 rows) by ONE tile
+//     of the round, so that a token fragment read from shared memory feeds four tensor-core
+//     instructions; with one row group per warp the kernel was bound by the shared-memory port, not
+//     by HBM;
 //   * the 2:4 gather is done by the tensor core: sign words are expanded in registers to fp16 +-1
 //     pairs (one shift + one logic op per pair, see the tile order in formats.h) and fed with the
 //     metadata words to mma.sp m16n8k32 with fp32 accumulation;
