@@ -68,7 +68,8 @@ class ShardedBinaryLinear:
     """
 
     def __init__(self, outfeatures: int, infeatures: int, group: Optional[dist.ProcessGroup] = None,
-                 matmul: Optional[Callable] = None, pack: Optional[Callable] = None, scatter: Optional[Callable] = None):
+                 matmul: Optional[Callable] = None, pack: Optional[Callable] = None, scatter: Optional[Callable] = None,
+                 peer_buffer: Optional[Callable] = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -79,6 +80,7 @@ class ShardedBinaryLinear:
         self.packed = None
         self._side = None
         self._scatter = scatter
+        self._peer_buffer = peer_buffer  # (layer, n, device) -> what _peer_mapped_buffer returns; for CPU ranks
         self._fused = {}                 # n -> (full C, peers' base addresses, keep-alive objects)
         self._flag = None
         self.fused_backend = None        # "symmetric_memory" or "ipc", once a fused buffer exists
@@ -166,6 +168,9 @@ class ShardedBinaryLinear:
         """A (m, n) fp16 buffer on every rank that all ranks can store to: returns (tensor, [base address
         of rank p's buffer as seen from this process], (handle, [tensor aliasing rank p's buffer]))."""
         shape = (self.m, n)
+        if self._peer_buffer is not None:
+            self.fused_backend = "injected"
+            return self._peer_buffer(self, n, dev)
         try:
             import torch.distributed._symmetric_memory as symm
             group = self.group if self.group is not None else dist.group.WORLD
@@ -227,20 +232,26 @@ class ShardedBinaryLinear:
         full, _, (_, views) = self._fused[n]
         mine = full[self.start:self.start + self.rows]
         peers = [p for p in range(self.world) if p != self.rank]
-        if self._push_streams is None:
+        cuda = dev.type == "cuda"
+        if cuda and self._push_streams is None:
             self._push_streams = [torch.cuda.Stream(device=dev) for _ in peers]
         self._rank_barrier(dev)                          # every rank is done reading the previous result
-        main = torch.cuda.current_stream(dev)
+        main = torch.cuda.current_stream(dev) if cuda else None
         for c0, crows in chunk_rows(self.rows, chunks):
             self._gemm(B, mine[c0:c0 + crows], c0, crows)
+            r0 = self.start + c0
+            if not cuda:
+                for p in peers:
+                    views[p][r0:r0 + crows].copy_(mine[c0:c0 + crows])
+                continue
             ready = torch.cuda.Event()
             ready.record(main)
-            r0 = self.start + c0
             for st, p in zip(self._push_streams, peers):
                 st.wait_event(ready)
                 with torch.cuda.stream(st):
                     views[p][r0:r0 + crows].copy_(mine[c0:c0 + crows], non_blocking=True)
-        for st in self._push_streams:
-            main.wait_stream(st)
+        if cuda:
+            for st in self._push_streams:
+                main.wait_stream(st)
         self._rank_barrier(dev)                          # every rank's copies have landed
         return full

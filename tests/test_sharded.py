@@ -58,7 +58,7 @@ def _free_port():
     return port
 
 
-def _cpu_worker(rank, world, port, mode, q):
+def _cpu_worker(rank, world, port, mode, q, shared_dir):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -77,11 +77,36 @@ def _cpu_worker(rank, world, port, mode, q):
             c32, _ = oracle.gemm(bits, meta, 0, Bt.numpy(), mm, scale=sc)
             out.copy_(torch.from_numpy(c32[row0:row0 + rows]))
 
-        layer = ShardedBinaryLinear(m, k, matmul=matmul, pack=pack)
+        def scatter(pw, Bt, mine, extra):                  # the several-destination GEMM: peers' rows by address
+            import ctypes
+            bits, meta, sc, mm = pw
+            c32, _ = oracle.gemm(bits, meta, 0, Bt.numpy(), mm, scale=sc)
+            mine.copy_(torch.from_numpy(c32))
+            src = mine.contiguous()
+            for addr in extra:
+                ctypes.memmove(addr, src.data_ptr(), src.numel() * src.element_size())
+
+        def peer_buffer(layer, nn, dev):                    # every rank's C in a file all ranks map
+            shape = (layer.m, nn)
+            paths = [os.path.join(shared_dir, f"c_{r}_{nn}.bin") for r in range(world)]
+            full = torch.from_file(paths[rank], shared=True, size=shape[0] * shape[1], dtype=torch.float16).view(shape)
+            dist.barrier()
+            views = [full if r == rank else torch.from_file(paths[r], shared=True, size=shape[0] * shape[1],
+                                                            dtype=torch.float16).view(shape) for r in range(world)]
+            return full, [v.data_ptr() for v in views], (None, views)
+
+        layer = ShardedBinaryLinear(m, k, matmul=matmul, pack=pack, scatter=scatter, peer_buffer=peer_buffer)
         layer.pack_full(torch.from_numpy(dense), torch.from_numpy(scale))
-        got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float32, chunks=2).numpy()
         canon, signs, _ = oracle.compress(dense)
         want, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), 0, B, m, scale=scale)
+        if mode in ("fused", "push"):
+            ok = True
+            for _ in range(2):                              # twice: the cached buffer is reused
+                got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float16, chunks=2).numpy()
+                ok &= bool((got == want.astype(np.float16)).all())
+            q.put((rank, ok, got.shape))
+            return
+        got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float32, chunks=2).numpy()
         if mode == "none":
             want = want[layer.start:layer.start + layer.rows]
         q.put((rank, bool((got == want).all()), got.shape))
@@ -89,12 +114,12 @@ def _cpu_worker(rank, world, port, mode, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["none", "all", "overlap"])
-def test_sharded_host_logic_two_cpu_ranks(mode):
+@pytest.mark.parametrize("mode", ["none", "all", "overlap", "fused", "push"])
+def test_sharded_host_logic_two_cpu_ranks(mode, tmp_path):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_cpu_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    procs = [ctx.Process(target=_cpu_worker, args=(r, 2, port, mode, q, str(tmp_path))) for r in range(2)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in procs]
