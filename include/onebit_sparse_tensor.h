@@ -46,7 +46,12 @@ enum { ONEBIT_OUT_F32 = 0, ONEBIT_OUT_F16 = 1 };
 enum { ONEBIT_DENSE_F16 = 0, ONEBIT_DENSE_BF16 = 1, ONEBIT_DENSE_I32 = 2 };
 enum { ONEBIT_KERNEL_AUTO = 0,    /* decode kernel for n <= 16 or n % 8 != 0, tensor-memory kernel otherwise */
        ONEBIT_KERNEL_PREFILL = 1, /* TMA + tcgen05.mma.sp kernel */
-       ONEBIT_KERNEL_DECODE = 2 };/* split-K cluster kernel for few tokens */
+       ONEBIT_KERNEL_DECODE = 2,  /* split-K cluster kernel for few tokens */
+       /* Flag, OR-ed into any of the above: the caller vouches that the packed weights of this call were
+        * complete before the kernel that precedes this call in `stream` was launched (weights packed at load
+        * time, as in a decode loop). The few-token kernel then requests them while that kernel still drains.
+        * Without the flag it requests nothing before that kernel has completed and its writes are visible. */
+       ONEBIT_KERNEL_STABLE_WEIGHTS = 0x100 };
 
 enum { ONEBIT_OK = 0, ONEBIT_ERR_SHAPE = 1, ONEBIT_ERR_NULL = 2, ONEBIT_ERR_CUDA = 3,
        ONEBIT_ERR_WORKSPACE = 4, ONEBIT_ERR_ARG = 5, ONEBIT_ERR_DEVICE_WAIT = 6 };
@@ -66,8 +71,12 @@ size_t onebit_workspace_bytes(int64_t m, int64_t k);
 /* Stateless GEMM on reference-ordered operands: the generalisation of onebit_sparse_matmul
  * (csrc/kernel_lib.cu:23-97) by a per-row scale (NULL = none), an fp16 output, a choice of metadata
  * order and a stream. Internally: relayout into `workspace`, then the dispatched kernel.
- * workspace == NULL makes the library use (and grow on demand) a per-device cached allocation,
- * which serialises concurrent calls on one device. Shapes the tiled kernels do not take
+ * workspace == NULL makes the library use one cached block per device, grown by cudaMalloc on demand
+ * and never freed while the process lives. Calls that share the block are ordered on the GPU by an
+ * event (each call's relayout waits for the previous call's GEMM), from whatever host threads and
+ * streams they come, so they are safe but do not overlap; pass per-stream workspaces for concurrency.
+ * Not usable on a stream that is being captured (ONEBIT_ERR_WORKSPACE): pass a workspace there.
+ * Shapes the tiled kernels do not take
  * (m % 128, k % 128 != 0; needs m % 32 == 0 (64 for ONEBIT_META_PYTHON), k % 32 == 0) run on a plain
  * CUDA-core kernel without workspace. stream is a cudaStream_t. */
 int onebit_sparse_matmul_ex(const void *a_bits, const void *b, void *d, const void *e_meta, const void *scale,
@@ -83,10 +92,11 @@ int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, in
 /* GEMM on tile-ordered operands (the fast path; the hot loop of BinaryLinear_2_4.forward,
  * onebit_sparse_mul/__init__.py:118-128). kernel: ONEBIT_KERNEL_*.
  * The few-token kernel is launched with programmatic stream serialisation: its grid may start while the
- * kernel before it in `stream` drains, and it requests the packed weights before it waits for that kernel
- * (tokens are read, and d is written, only afterwards). Kernels of this library hand over early only after
- * their own weight requests are out and never produce packed weights; any other kernel hands over when it
- * has completed. Set ONEBIT_PDL=0 in the environment to launch it as an ordinary kernel. */
+ * kernel before it in `stream` drains. By default it touches no operand before that kernel has completed
+ * (a producer such as onebit_relayout or onebit_pack_from_dense may sit directly before it). With
+ * ONEBIT_KERNEL_STABLE_WEIGHTS it requests the packed weights first and waits only then; tokens are read,
+ * and d is written, after the wait in either case. Set ONEBIT_PDL=0 in the environment to launch it as an
+ * ordinary kernel. */
 int onebit_matmul_packed(const void *bits_tile, const void *meta_tile, const void *scale, const void *b, void *d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
@@ -109,7 +119,7 @@ int onebit_matmul_packed_scatter(const void *bits_tile, const void *meta_tile, c
  * (tests/python/test_model_replace.py:22-44; its forward passes x straight through,
  * onebit_sparse_mul/__init__.py:118-128). n <= 16 runs on the split-K cluster kernel, more tokens on
  * the CTA-pair tensor-memory kernel (needs m % 256 == 0; otherwise the cluster kernel serves any n).
- * x must be 16-byte aligned. kernel: ONEBIT_KERNEL_*. */
+ * x must be 16-byte aligned. kernel: ONEBIT_KERNEL_* (ONEBIT_KERNEL_STABLE_WEIGHTS as above). */
 int onebit_linear_tokens(const void *bits_tile, const void *meta_tile, const void *scale, const void *bias, const void *x,
                          void *y, int64_t m, int64_t n, int64_t k, int out_type, int kernel, void *stream);
 
@@ -120,8 +130,10 @@ int onebit_linear_tokens(const void *bits_tile, const void *meta_tile, const voi
  * three-slot pipeline on internal streams, so a call costs about max(H2D, D2H). `workspace` is DEVICE
  * memory of onebit_host_workspace_bytes(m, n, k, out_type) bytes, 256-byte aligned, owned by the caller
  * and busy until the work queued by this call has finished. Asynchronous like the other calls: work
- * queued on `stream` before the call precedes it, work queued after it follows it. Concurrent calls on
- * one device share the internal streams and therefore serialise. Needs n % 8 == 0. */
+ * queued on `stream` before the call precedes it, work queued after it follows it. Calls on one device
+ * share three internal streams: a call is enqueued as a whole under a lock, and a later call's legs queue
+ * behind the earlier call's on those streams, so concurrent callers are safe and serialise. Each call
+ * that may overlap another needs its own workspace. Needs n % 8 == 0. */
 size_t onebit_host_workspace_bytes(int64_t m, int64_t n, int64_t k, int out_type);
 int onebit_matmul_packed_host(const void *bits_tile, const void *meta_tile, const void *scale, const void *b_host,
                               void *d_host, int64_t m, int64_t n, int64_t k, int out_type, void *workspace,
@@ -159,9 +171,12 @@ int onebit_unpack_to_dense(const void *bits_tile, const void *meta_tile, const v
  * the library image (held by every GPU that loads the library, until exit) instead of a workspace:
  *   - m * k <= ONEBIT_STATIC_MAX_WEIGHTS, m % 128 == 0, k % 128 == 0, else an error and no launch;
  *   - always the split-K cluster kernel (meant for few tokens; any n works);
- *   - the first call per device fetches the array's device address: make it outside stream capture;
+ *   - the first call per device looks up the array's device address, and with CUDA's lazy module loading
+ *     that look-up is also the moment the driver loads this part of the library and reserves the array
+ *     (about 8 MiB): make one warm-up call per device at start-up, outside stream capture, while device
+ *     memory is still available. Later calls touch no allocator;
  *   - calls share the array: two calls that overlap on the GPU race -- serialise them;
- *   - never calls cudaMalloc / cudaFree or an allocating library routine. */
+ *   - calls no cudaMalloc / cudaFree or allocating library routine. */
 #define ONEBIT_STATIC_MAX_WEIGHTS (4096LL * 11008LL)
 int onebit_sparse_matmul_static(const void *a_bits, const void *b, void *d, const void *e_meta, const void *scale,
                                 int64_t m, int64_t n, int64_t k, int out_type, int meta_dialect, void *stream);

@@ -10,8 +10,8 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from ._lib import (DENSE_BF16, DENSE_F16, DENSE_I32, KERNEL_AUTO, KERNEL_DECODE, KERNEL_PREFILL, META_CUTLASS,
-                   META_PYTHON, OUT_F16, OUT_F32, OneBitError)
+from ._lib import (DENSE_BF16, DENSE_F16, DENSE_I32, KERNEL_AUTO, KERNEL_DECODE, KERNEL_PREFILL, KERNEL_STABLE_WEIGHTS,
+                   META_CUTLASS, META_PYTHON, OUT_F16, OUT_F32, OneBitError)
 from ._semi_structured_conversions import (mask_creator, sparse_semi_structured_from_dense_cutlass,
                                            sparse_semi_structured_to_dense_cutlass)
 
@@ -137,12 +137,25 @@ def py_binary_gemm(x, packed_sparse_tensor, sparse_meta):
 # ---- tile-ordered weights: the fast path ---------------------------------------------------------------
 
 class PackedWeight:
-    """A weight matrix in this library's streaming order plus its reference-ordered twin."""
+    """A weight matrix in this library's streaming order plus its reference-ordered twin.
 
-    def __init__(self, m, k, bits_tile, meta_tile, scale=None, packed_binary_sparse=None, meta=None):
+    ``stable`` says that the packed tensors were complete before the kernel that precedes the next GEMM in
+    the stream was launched; the few-token kernel may then request them early
+    (``ONEBIT_KERNEL_STABLE_WEIGHTS``). A new object starts out not stable -- the kernel that wrote it may
+    be the one right before its first GEMM -- and becomes stable with that first GEMM. Code that rewrites
+    the tensors in place must reset the attribute."""
+
+    def __init__(self, m, k, bits_tile, meta_tile, scale=None, packed_binary_sparse=None, meta=None, stable=False):
         self.m, self.k = m, k
         self.bits_tile, self.meta_tile, self.scale = bits_tile, meta_tile, scale
         self.packed_binary_sparse, self.meta = packed_binary_sparse, meta
+        self.stable = stable
+
+    def _selector(self, kernel):
+        """The kernel selector of the next GEMM on these weights, with the stable-weights flag."""
+        flag = KERNEL_STABLE_WEIGHTS if self.stable else 0
+        self.stable = True
+        return kernel | flag
 
 
 def pack_weight(weight, scale=None, apply_mask=True, keep_reference=True, meta_dialect=META_PYTHON) -> PackedWeight:
@@ -197,7 +210,7 @@ def matmul_packed(pw: PackedWeight, B, out=None, out_dtype=torch.float32, kernel
         out = torch.empty((pw.m, n), dtype=out_dtype, device=B.device)
     with torch.cuda.device(B.device):
         _lib.check(lib.onebit_matmul_packed(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(B), _ptr(out),
-                                            pw.m, n, pw.k, _out_code(out.dtype), kernel, _stream()))
+                                            pw.m, n, pw.k, _out_code(out.dtype), pw._selector(kernel), _stream()))
     return out
 
 
@@ -214,7 +227,7 @@ def linear_tokens(pw: PackedWeight, x, bias=None, out_dtype=torch.float16, kerne
     if n > 0:
         with torch.cuda.device(x.device):
             _lib.check(lib.onebit_linear_tokens(_ptr(pw.bits_tile), _ptr(pw.meta_tile), _ptr(pw.scale), _ptr(bias), _ptr(x2),
-                                                _ptr(y), pw.m, n, pw.k, _out_code(out_dtype), kernel, _stream()))
+                                                _ptr(y), pw.m, n, pw.k, _out_code(out_dtype), pw._selector(kernel), _stream()))
     return y.reshape(*lead, pw.m)
 
 
@@ -264,7 +277,8 @@ def matmul_rows(pw: PackedWeight, B, out, row0: int, rows: int, kernel=KERNEL_AU
     scale_ptr = None if pw.scale is None else pw.scale.data_ptr() + 2 * row0
     with torch.cuda.device(B.device):
         _lib.check(lib.onebit_matmul_packed(pw.bits_tile.data_ptr() + tiles * 1024, pw.meta_tile.data_ptr() + tiles * 2048,
-                                            scale_ptr, _ptr(B), _ptr(out), rows, n, pw.k, _out_code(out.dtype), kernel, _stream()))
+                                            scale_ptr, _ptr(B), _ptr(out), rows, n, pw.k, _out_code(out.dtype),
+                                            pw._selector(kernel), _stream()))
     return out
 
 
@@ -314,14 +328,23 @@ class BinaryLinear_2_4(nn.Module):
         self.register_buffer("bias", torch.zeros(outfeatures, dtype=torch.float16) if bias else None)
         self.register_buffer("packed_flag", torch.zeros((), dtype=torch.uint8))     # makes `vaild` survive state_dict
         self.vaild = False                # (sic) the reference's attribute name, __init__.py:117
+        self._weights_stable = False      # see PackedWeight.stable; reset whenever the buffers are rewritten
 
     def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
         self.vaild = bool(self.packed_flag.item())
+        self._weights_stable = False
+
+    def _apply(self, fn, *args, **kwargs):
+        self._weights_stable = False      # .to() / .cuda() copy the buffers with kernels of the current stream
+        return super()._apply(fn, *args, **kwargs)
 
     def _packed(self):
         # the scale defaults to ones: multiplying by 1 is exact, so an unscaled layer equals the reference's
-        return PackedWeight(self.outfeatures, self.infeatures, self.bits_tile, self.meta_tile, self.scale)
+        pw = PackedWeight(self.outfeatures, self.infeatures, self.bits_tile, self.meta_tile, self.scale,
+                          stable=self._weights_stable)
+        self._weights_stable = True
+        return pw
 
     def forward(self, x):
         """x: (infeatures, tokens) fp16 on the layer's device -> (outfeatures, tokens)."""
@@ -350,6 +373,7 @@ class BinaryLinear_2_4(nn.Module):
             self.bias = bias.detach().to(dev, torch.float16).clone()
         self.packed_flag = torch.ones((), dtype=torch.uint8, device=dev)
         self.vaild = True
+        self._weights_stable = False
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, out_dtype=torch.float16) -> "BinaryLinear_2_4":

@@ -15,6 +15,7 @@ META_PYTHON, META_CUTLASS = 0, 1
 OUT_F32, OUT_F16 = 0, 1
 DENSE_F16, DENSE_BF16, DENSE_I32 = 0, 1, 2
 KERNEL_AUTO, KERNEL_PREFILL, KERNEL_DECODE = 0, 1, 2
+KERNEL_STABLE_WEIGHTS = 0x100     # flag OR-ed into a kernel selector (see the header)
 
 # every extern "C" symbol of include/onebit_sparse_tensor.h, with its ctypes signature
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t

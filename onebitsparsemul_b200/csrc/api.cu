@@ -41,26 +41,36 @@ size_t round256(size_t x) { return (x + 255) & ~size_t(255); }
 
 bool tiled_shape(int64_t m, int64_t k) { return m > 0 && k > 0 && m % OB_TILE_M == 0 && k % OB_TILE_K == 0; }
 
-// Per-device scratch owned by the library: the relayout target of the stateless entry points and
-// the status word of the tensor-memory kernel. Grown on demand, never shrunk, freed at process
-// exit by the driver.
+// Per-device state owned by the library: the status word of the tensor-memory kernels and the relayout
+// scratch of the stateless entry points when the caller passes no workspace. The scratch is grown on
+// demand and never freed or shrunk while the process lives: a block that was outgrown may still be read by
+// launches already queued, so it is only retired. Calls that share it are ordered on the GPU by `last_use`
+// (recorded after each call's GEMM, waited on before the next call's relayout), whatever streams they use.
 struct DeviceScratch {
   void* buf = nullptr;
   size_t bytes = 0;
   int* status = nullptr;
+  cudaEvent_t last_use = nullptr;
+  int sms = 0;
 };
-std::mutex g_mu;
+std::mutex g_mu;           // guards the fields of g_scratch
+std::mutex g_scratch_mu;   // held for the whole enqueue of a call that uses the library-owned scratch block
 DeviceScratch g_scratch[64];
+
+int current_device(int* dev) {
+  cudaError_t e = cudaGetDevice(dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (*dev < 0 || *dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal %d not supported", *dev);
+  return ONEBIT_OK;
+}
 
 int get_status_word(int** out) {
   int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal %d not supported", dev);
+  if (int rc = current_device(&dev)) return rc;
   std::lock_guard<std::mutex> lk(g_mu);
   DeviceScratch& s = g_scratch[dev];
   if (!s.status) {
-    e = cudaMalloc(&s.status, sizeof(int));
+    cudaError_t e = cudaMalloc(&s.status, sizeof(int));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(status)");
     e = cudaMemset(s.status, 0, sizeof(int));
     if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(status)");
@@ -69,27 +79,18 @@ int get_status_word(int** out) {
   return ONEBIT_OK;
 }
 
-int get_scratch(size_t bytes, void** out) {
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal %d not supported", dev);
-  std::lock_guard<std::mutex> lk(g_mu);
-  DeviceScratch& s = g_scratch[dev];
-  if (s.bytes < bytes) {
-    if (s.buf) {
-      // earlier launches may still read the old buffer
-      e = cudaDeviceSynchronize();
-      if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
-      cudaFree(s.buf);
-      s.buf = nullptr;
-      s.bytes = 0;
-    }
-    e = cudaMalloc(&s.buf, bytes);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(scratch)");
-    s.bytes = bytes;
+// Called with g_scratch_mu held. Makes the device's scratch at least `bytes` large.
+int grow_scratch_locked(DeviceScratch& s, size_t bytes) {
+  if (!s.last_use) {
+    cudaError_t e = cudaEventCreateWithFlags(&s.last_use, cudaEventDisableTiming);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
   }
-  *out = s.buf;
+  if (s.bytes >= bytes) return ONEBIT_OK;
+  void* fresh = nullptr;
+  cudaError_t e = cudaMalloc(&fresh, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(scratch)");
+  s.buf = fresh;      // the outgrown block stays allocated: queued launches may still read it
+  s.bytes = bytes;
   return ONEBIT_OK;
 }
 
@@ -102,7 +103,11 @@ int check_dialect_rows(int dialect, int64_t m) {
 }
 
 int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
-                       int64_t m, int64_t n, int64_t k, int out_type, int kernel, bool fresh_weights, cudaStream_t stream) {
+                       int64_t m, int64_t n, int64_t k, int out_type, int kernel, cudaStream_t stream) {
+  // unless the caller vouches for the age of the packed weights, the few-token kernel requests them only
+  // after the kernel before it in the stream has completed
+  const bool fresh_weights = (kernel & ONEBIT_KERNEL_STABLE_WEIGHTS) == 0;
+  kernel &= ~ONEBIT_KERNEL_STABLE_WEIGHTS;
   if (!bits_tile || !meta_tile || !b || !d) return fail(ONEBIT_ERR_NULL, "null operand pointer");
   if (!tiled_shape(m, k) || n < 1)
     return fail(ONEBIT_ERR_SHAPE, "tile-ordered GEMM needs m %% 128 == 0, k %% 128 == 0, n >= 1 (got m=%lld n=%lld k=%lld)",
@@ -132,6 +137,15 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
 namespace ob {
 // lets the other translation units of the library report through onebit_last_error()
 void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceScratch& s = g_scratch[dev];
+  if (s.sms == 0 && cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) s.sms = 0;
+  return s.sms > 0 ? s.sms : 148;
+}
 }  // namespace ob
 
 extern "C" {
@@ -155,7 +169,7 @@ int onebit_relayout(const void* a_bits, const void* e_meta, int meta_dialect, in
 
 int onebit_matmul_packed(const void* bits_tile, const void* meta_tile, const void* scale, const void* b, void* d,
                          int64_t m, int64_t n, int64_t k, int out_type, int kernel, void* stream) {
-  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, false, static_cast<cudaStream_t>(stream));
+  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, kernel, static_cast<cudaStream_t>(stream));
 }
 
 int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias, const void* x,
@@ -167,6 +181,8 @@ int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const voi
   if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type %d", out_type);
   if (reinterpret_cast<uintptr_t>(x) & 15) return fail(ONEBIT_ERR_ARG, "x must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fresh_weights = (kernel & ONEBIT_KERNEL_STABLE_WEIGHTS) == 0;
+  kernel &= ~ONEBIT_KERNEL_STABLE_WEIGHTS;
   if (kernel == ONEBIT_KERNEL_AUTO)
     kernel = (n > 16 && ob::prefill_tokens_supported(m, n, k)) ? ONEBIT_KERNEL_PREFILL : ONEBIT_KERNEL_DECODE;
   cudaError_t e;
@@ -178,7 +194,7 @@ int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const voi
     e = ob::launch_gemm_prefill_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, status, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, st);
+    e = ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, fresh_weights, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major decode GEMM launch");
   } else {
     return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
@@ -220,17 +236,40 @@ int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const vo
     return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "plain GEMM launch");
   }
   const size_t need = onebit_workspace_bytes(m, k);
+  const size_t bits_bytes = round256(onebit_packed_bits_bytes(m, k));
   if (workspace) {
     if (workspace_bytes < need) return fail(ONEBIT_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
     if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return fail(ONEBIT_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-  } else {
-    if (int rc = get_scratch(need, &workspace)) return rc;
+    void* bits_tile = workspace;
+    void* meta_tile = static_cast<char*>(workspace) + bits_bytes;
+    cudaError_t e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
+    if (e != cudaSuccess) return cuda_fail(e, "relayout launch");
+    return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, st);
   }
-  void* bits_tile = workspace;
-  void* meta_tile = static_cast<char*>(workspace) + round256(onebit_packed_bits_bytes(m, k));
-  cudaError_t e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
+  // Library-owned scratch: one block per device, shared by every such call. The whole enqueue happens under
+  // the lock and between a wait on and a record of the block's event, so concurrent calls -- other host
+  // threads, other streams -- use the block one after the other on the GPU.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(st, &cap);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamIsCapturing");
+  if (cap != cudaStreamCaptureStatusNone)
+    return fail(ONEBIT_ERR_WORKSPACE, "a stream that is being captured needs a caller-provided workspace (the library's own "
+                                      "scratch may have to grow, and is ordered by an event outside the capture)");
+  int dev = 0;
+  if (int rc = current_device(&dev)) return rc;
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  DeviceScratch& s = g_scratch[dev];
+  if (int rc = grow_scratch_locked(s, need)) return rc;
+  void* bits_tile = s.buf;
+  void* meta_tile = static_cast<char*>(s.buf) + bits_bytes;
+  e = cudaStreamWaitEvent(st, s.last_use, 0);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent(scratch)");
+  e = ob::launch_relayout(a_bits, e_meta, meta_dialect, m, k, bits_tile, meta_tile, st);
   if (e != cudaSuccess) return cuda_fail(e, "relayout launch");
-  return matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, /*fresh_weights=*/true, st);
+  const int rc = matmul_packed_impl(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, ONEBIT_KERNEL_AUTO, st);
+  e = cudaEventRecord(s.last_use, st);   // also after a failed GEMM launch: the relayout already uses the block
+  if (rc != ONEBIT_OK) return rc;
+  return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "cudaEventRecord(scratch)");
 }
 
 int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits,

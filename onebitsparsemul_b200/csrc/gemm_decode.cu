@@ -159,6 +159,9 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
     for (int r = 0; r < npre; ++r) issue(r);
   }
   __syncwarp();
+  // Every CTA of the cluster announces that it runs; the matching wait stands right before the first store into
+  // another CTA's shared memory, which must not be touched before that CTA has started.
+  if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may begin its own prologue
   asm volatile("griddepcontrol.wait;" ::: "memory");                // the previous kernel's results (the tokens) are complete
   OB_TRACE_EV(1);
@@ -172,8 +175,10 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
       for (int i = 0; i < 4; ++i) acc[rg][nt][i] = 0.f;
 
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
-  // one token (n == 1) in the reference layout is the same contiguous vector as a token-major row
-  const bool rows_contiguous = TM || a.n == 1;
+  // one token (n == 1) in the reference layout is the same contiguous vector as a token-major row; the
+  // 16-byte loads of that form need an aligned base (token-major callers are checked on the host), any
+  // other single token takes the element-wise path below
+  const bool rows_contiguous = TM || (a.n == 1 && (reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
   const bool quad_rows = !rows_contiguous && (a.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 7) == 0);
   const bool vec_rows = !rows_contiguous && (a.n % 8 == 0) && (nvalid == NP) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
 
@@ -345,6 +350,7 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
   constexpr int kQuads = 128 * NP / 4;                        // = NT * kThreads
   const int rows_per = 128 / S;                               // S is a power of two
   cg::cluster_group cluster = cg::this_cluster();
+  if (S > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // all CTAs of the cluster have started
 #pragma unroll
   for (int i = 0; i < kQuads / kThreads; ++i) {
     const int x = tid + i * kThreads;
@@ -441,11 +447,12 @@ namespace {
 // holds two CTAs: S minimises rounds x CTAs per SM among the splits that keep the grid one wave.
 int pick_split(int64_t m, int64_t k, int lanes) {
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
+  const int sms = ob::sm_count();
   int best = 1;
   long long best_cost = LLONG_MAX;
   for (int S = 1; S <= 8; S *= 2) {
-    if (S > 1 && (row_blocks * S > 2 * 148 || tiles_k < S)) break;
-    const long long T = (tiles_k + S - 1) / S, rounds = (T + lanes - 1) / lanes, per_sm = (row_blocks * S + 147) / 148;
+    if (S > 1 && (row_blocks * S > 2 * sms || tiles_k < S)) break;
+    const long long T = (tiles_k + S - 1) / S, rounds = (T + lanes - 1) / lanes, per_sm = (row_blocks * S + sms - 1) / sms;
     if (rounds * per_sm <= best_cost) { best = S; best_cost = rounds * per_sm; }   // ties: more CTAs stream
   }
   // tuning knob for experiments
@@ -472,9 +479,10 @@ cudaError_t launch_gemm_decode(const void* bits_tile, const void* meta_tile, con
 
 cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
-                                      cudaStream_t stream) {
+                                      bool fresh_weights, cudaStream_t stream) {
   DecodeArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
-               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(x), y, m, n, k, 0};
+               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(x), y, m, n, k,
+               fresh_weights ? 1 : 0};
   return dispatch<true>(a, out_type, stream);
 }
 

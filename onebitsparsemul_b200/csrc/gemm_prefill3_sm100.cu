@@ -323,17 +323,14 @@ template <bool TM, bool MULTI>
 cudaError_t launch3(const CUtensorMap& tmap, const Prefill3Args& a, cudaStream_t stream) {
   using C = Cfg3;
   static bool configured[64] = {};
-  static int sm_count[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(ob_gemm_prefill3_kernel<TM, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
-    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int sms = dev < 64 ? sm_count[dev] : 148;
+  const int sms = ob::sm_count();
   const int clusters = std::min(a.total_tiles, std::max(1, sms / 2));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * clusters));

@@ -367,9 +367,10 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   const int forced = forced_variant();
   const int64_t row_tiles = m / BM;
   const bool two = (m % 256 == 0);
+  const int sms = sm_count();
   // The CTA-pair kernel (256 rows x 256 tokens per pair, each CTA staging half of the token tile) is
-  // the fastest once its pairs fill the 74 SM pairs.
-  const bool pair_fits = n > 128 && prefill2_supported(m, n, k) && (row_tiles / 2) * ((n + 255) / 256) >= 74;
+  // the fastest once its pairs fill the SM pairs of the chip.
+  const bool pair_fits = n > 128 && prefill2_supported(m, n, k) && (row_tiles / 2) * ((n + 255) / 256) >= sms / 2;
   // Its persistent form saves the per-tile start-up (tensor-memory allocation, barrier set-up, first ring
   // of loads) and overlaps the output stores with the next tile: measured +4 % (k = 4096) to +39 %
   // (k = 1024) for short k loops, -1 % to -5 % for k >= 8192, where the stores through TMA win.
@@ -407,10 +408,10 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
     default: break;
   }
   // Single-CTA variants, all with the +-1 operand in tensor memory: a 256-token tile once it fills
-  // the 148 SMs, else two stacked weight tiles sharing 128 tokens, else the smallest tile, which
+  // the SMs, else two stacked weight tiles sharing 128 tokens, else the smallest tile, which
   // spreads a small problem over the most SMs.
-  if (n > 128 && row_tiles * ((n + 255) / 256) >= 148) return launch<1, 256, 1, true>(tmap, a, stream);
-  if (two && (row_tiles / 2) * ((n + 127) / 128) >= 148) return launch<2, 128, 1, true>(tmap, a, stream);
+  if (n > 128 && row_tiles * ((n + 255) / 256) >= sms) return launch<1, 256, 1, true>(tmap, a, stream);
+  if (two && (row_tiles / 2) * ((n + 127) / 128) >= sms) return launch<2, 128, 1, true>(tmap, a, stream);
   return launch<1, 128, 1, true>(tmap, a, stream);
 }
 

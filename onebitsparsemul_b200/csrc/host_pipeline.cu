@@ -77,10 +77,11 @@ extern "C" int onebit_matmul_packed_host(const void* bits_tile, const void* meta
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
   if (dev < 0 || dev >= 64) return fail(ONEBIT_ERR_ARG, "device ordinal not supported");
-  DevicePipes* P;
+  // The lock is held for the whole enqueue: the per-device streams and events are shared, and records and
+  // waits of two interleaved calls would pair up wrongly.
+  std::lock_guard<std::mutex> lk(g_mu);
+  DevicePipes* P = &g_pipes[dev];
   {
-    std::lock_guard<std::mutex> lk(g_mu);
-    P = &g_pipes[dev];
     if (!P->ready) {
       cudaStream_t* ss[3] = {&P->in, &P->compute, &P->out};
       for (auto s : ss) if ((e = cudaStreamCreateWithFlags(s, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
@@ -108,33 +109,41 @@ extern "C" int onebit_matmul_packed_host(const void* bits_tile, const void* meta
   cudaStreamWaitEvent(P->in, P->start, 0);
   cudaStreamWaitEvent(P->compute, P->start, 0);
   cudaStreamWaitEvent(P->out, P->start, 0);
+  // the caller's stream continues when all three internal streams have run dry: the last result panel is
+  // home and nothing reads the slots any more. Also used on the error paths, so that whatever was queued
+  // before a failure is still ordered before the caller's later work.
+  auto join = [&] {
+    cudaStream_t legs[3] = {P->in, P->compute, P->out};
+    for (cudaStream_t leg : legs) {
+      cudaEventRecord(P->done, leg);
+      cudaStreamWaitEvent(user, P->done, 0);
+    }
+  };
 
   for (int64_t p = 0; p < panels; ++p) {
     const int s = (int)(p % kSlots);
     const int64_t c0 = p * np, w = std::min(np, n - c0);
-    // host -> device, pitched: k rows of w tokens; the slot must have been drained by panel p - kSlots
-    if (p >= kSlots) cudaStreamWaitEvent(P->in, P->computed[s], 0);
+    // host -> device, pitched: k rows of w tokens. The slot's previous user -- panel p - kSlots, or a panel of
+    // the previous call on this device, which may have come from another stream with the same workspace --
+    // must have been multiplied (an event that was never recorded does not hold anything up)
+    cudaStreamWaitEvent(P->in, P->computed[s], 0);
     e = cudaMemcpy2DAsync(b_dev(s), (size_t)w * 2, static_cast<const char*>(b_host) + (size_t)c0 * 2, (size_t)n * 2,
                           (size_t)w * 2, (size_t)k, cudaMemcpyHostToDevice, P->in);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy2DAsync(H2D)");
+    if (e != cudaSuccess) { join(); return cuda_fail(e, "cudaMemcpy2DAsync(H2D)"); }
     cudaEventRecord(P->loaded[s], P->in);
     // GEMM on the panel (the dispatcher picks the kernel for its width)
     cudaStreamWaitEvent(P->compute, P->loaded[s], 0);
-    if (p >= kSlots) cudaStreamWaitEvent(P->compute, P->drained[s], 0);
+    cudaStreamWaitEvent(P->compute, P->drained[s], 0);      // and its result must have left the slot
     const int rc = onebit_matmul_packed(bits_tile, meta_tile, scale, b_dev(s), c_dev(s), m, w, k, out_type, ONEBIT_KERNEL_AUTO, P->compute);
-    if (rc != ONEBIT_OK) return rc;
+    if (rc != ONEBIT_OK) { join(); return rc; }
     cudaEventRecord(P->computed[s], P->compute);
     // device -> host, pitched
     cudaStreamWaitEvent(P->out, P->computed[s], 0);
     e = cudaMemcpy2DAsync(static_cast<char*>(d_host) + (size_t)c0 * esz, (size_t)n * esz, c_dev(s), (size_t)w * esz,
                           (size_t)w * esz, (size_t)m, cudaMemcpyDeviceToHost, P->out);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy2DAsync(D2H)");
+    if (e != cudaSuccess) { join(); return cuda_fail(e, "cudaMemcpy2DAsync(D2H)"); }
     cudaEventRecord(P->drained[s], P->out);
   }
-  // the caller's stream continues when the last result panel is home (and all reads of the slots are done)
-  cudaEventRecord(P->done, P->out);
-  cudaStreamWaitEvent(user, P->done, 0);
-  cudaEventRecord(P->done, P->compute);
-  cudaStreamWaitEvent(user, P->done, 0);
+  join();
   return ONEBIT_OK;
 }

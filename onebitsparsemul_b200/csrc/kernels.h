@@ -5,6 +5,9 @@
 
 namespace ob {
 
+// Multiprocessors of the current device (cached per device; the dispatchers size their grids by it).
+int sm_count();
+
 // K1 (pack.cu)
 cudaError_t launch_pack(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse,
                         void* bits_ref, void* meta_ref, int dialect, void* bits_tile, void* meta_tile,
@@ -45,7 +48,7 @@ cudaError_t launch_gemm_prefill_scatter(const void* bits_tile, const void* meta_
 bool prefill_scatter_supported(int64_t m, int64_t n, int64_t k, const void* d);
 cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                       const void* x, void* y, int64_t m, int64_t n, int64_t k, int out_type,
-                                      cudaStream_t stream);
+                                      bool fresh_weights, cudaStream_t stream);
 // Reads and clears the decode kernel's bounded-wait status on the current device (0 = nothing gave up).
 cudaError_t read_decode_status(int* out);
 

@@ -6,8 +6,11 @@
 // or a host that forbids allocation after start-up. The other stateless entry point either takes a
 // caller-provided workspace or grows a cached cudaMalloc'ed one; this one does neither. Its relayout
 // target (the tile-ordered copy of the weights that the GEMM kernel reads) is a fixed array that is
-// part of the library image: every GPU that loads libonebitmul holds these ~8 MiB until the process
-// exits, whether or not this function is ever called.
+// part of the library image: a GPU holds these ~8 MiB from the moment the driver loads this part of
+// the library on it until the process exits. With CUDA's default lazy module loading that moment is the
+// first call of this function on the device (the address look-up below), with eager loading it is the
+// creation of the context; so the first call per device belongs into start-up, as a warm-up, while device
+// memory is still to be had -- it can fail like an allocation. Every later call touches no allocator.
 //
 // Limits and rules
 //   * m * k <= ONEBIT_STATIC_MAX_WEIGHTS (4096 x 11008, the largest 7B-class decode layer); larger
@@ -15,12 +18,14 @@
 //   * Shapes must be tile-shaped (m % 128 == 0, k % 128 == 0); the GEMM always runs on the split-K
 //     cluster kernel (any n; meant for few tokens).
 //   * The first call on each device looks up the array's device address (once per device, with that
-//     device current). Make that first call outside any stream capture.
+//     device current) and thereby may make the driver load the module and reserve the array. Make that
+//     first call at start-up, outside any stream capture.
 //   * All calls on a device share the one array, and it keeps the previous call's contents. Every
 //     byte the GEMM reads is rewritten by the relayout of the same call, so nothing needs clearing,
 //     but two calls whose kernels overlap on the GPU (different streams, no dependency) race on it:
 //     serialise them.
-//   * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
+//   * No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later (the
+//     test watches cudaMemGetInfo across the later calls).
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -58,10 +63,12 @@ extern "C" int onebit_sparse_matmul_static(const void* a_bits, const void* b, vo
     return fail(ONEBIT_ERR_SHAPE, "onebit_sparse_matmul_static needs m % 128 == 0, k % 128 == 0, n >= 1");
   if (meta_dialect != OB_META_PYTHON && meta_dialect != OB_META_CUTLASS) return fail(ONEBIT_ERR_ARG, "unknown metadata order");
   if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type");
-  if ((uint64_t)m * (uint64_t)k > (uint64_t)ONEBIT_STATIC_MAX_WEIGHTS) {
+  // m and k are bounded one by one first, so that the product cannot wrap
+  if (m > ONEBIT_STATIC_MAX_WEIGHTS / OB_TILE_K || k > ONEBIT_STATIC_MAX_WEIGHTS / OB_TILE_M ||
+      (uint64_t)m * (uint64_t)k > (uint64_t)ONEBIT_STATIC_MAX_WEIGHTS) {
     snprintf(g_msg, sizeof(g_msg),
              "onebit_sparse_matmul_static: m*k = %lld exceeds the built-in scratch (%lld weights); use "
-             "onebit_sparse_matmul_ex with a workspace", (long long)(m * k), (long long)ONEBIT_STATIC_MAX_WEIGHTS);
+             "onebit_sparse_matmul_ex with a workspace", (long long)((double)m * (double)k), (long long)ONEBIT_STATIC_MAX_WEIGHTS);
     return fail(ONEBIT_ERR_WORKSPACE, g_msg);
   }
   int dev = 0;

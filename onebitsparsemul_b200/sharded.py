@@ -8,13 +8,8 @@ slab. The reference has no multi-GPU code; this module is the only place a colle
 only when the caller asks for the full C on every rank:
 
   gather="none"     each rank returns its (rows_g, n) slab                      (no collective)
-  gather="all"      one NCCL all-gather after the GEMM
-  gather="overlap"  the slab is computed in row chunks; chunk c travels (grouped send/recv into the
-                    right rows of the full C) on a side stream while chunk c+1 is computed
-  gather="push"     the slab is computed in row chunks; as soon as a chunk is done, the copy engines push it
-                    into the same rows of every other rank's C (plain device-to-device copies to peer-mapped
-                    memory, one side stream per peer) while the next chunk is multiplied. No SM is spent on
-                    communication. Same cached peer-mapped C and rank ordering as "fused".
+  gather="all"      one NCCL all-gather after the GEMM (one grouped send/recv exchange when the slabs
+                    are of unequal height)
   gather="fused"    no collective kernel at all: the GEMM's epilogue stores every output tile into this
                     rank's C and, through peer-mapped memory, into the same rows of every other rank's C
                     while the next tile is multiplied (``onebit_matmul_packed_scatter``). C lives in a
@@ -54,12 +49,6 @@ def row_partition(m: int, world: int, block: int = ROW_BLOCK) -> List[Tuple[int,
     return out
 
 
-def chunk_rows(rows: int, chunks: int, block: int = ROW_BLOCK) -> List[Tuple[int, int]]:
-    """Split a slab into at most `chunks` row chunks of whole blocks."""
-    chunks = max(1, min(chunks, rows // block))
-    return row_partition(rows, chunks, block)
-
-
 class ShardedBinaryLinear:
     """One rank's share of a row-sharded one-bit 2:4 layer.
 
@@ -78,13 +67,11 @@ class ShardedBinaryLinear:
         self.start, self.rows = self.partition[self.rank]
         self._matmul, self._pack = matmul, pack
         self.packed = None
-        self._side = None
         self._scatter = scatter
         self._peer_buffer = peer_buffer  # (layer, n, device) -> what _peer_mapped_buffer returns; for CPU ranks
         self._fused = {}                 # n -> (full C, peers' base addresses, keep-alive objects)
         self._flag = None
         self.fused_backend = None        # "symmetric_memory" or "ipc", once a fused buffer exists
-        self._push_streams = None
 
     # -- weights ---------------------------------------------------------------------------------------
     def pack_slab(self, weight_slab, scale_slab=None, apply_mask=True):
@@ -111,7 +98,7 @@ class ShardedBinaryLinear:
         from . import matmul_rows
         return matmul_rows(self.packed, B, out, row0, rows)
 
-    def forward(self, B, gather: str = "none", out_dtype=torch.float16, chunks: int = 4):
+    def forward(self, B, gather: str = "none", out_dtype=torch.float16):
         n = B.shape[1]
         dev = B.device
         if gather == "none" or self.world == 1:
@@ -120,47 +107,23 @@ class ShardedBinaryLinear:
             return out
         if gather == "fused":
             return self._forward_fused(B, out_dtype)
-        if gather == "push":
-            return self._forward_push(B, out_dtype, chunks)
+        if gather != "all":
+            raise ValueError(f"unknown gather mode {gather!r}")
         full = torch.empty((self.m, n), dtype=out_dtype, device=dev)
         mine = full[self.start:self.start + self.rows]
-        if gather == "all" and len({r for _, r in self.partition}) == 1:
-            self._gemm(B, mine)
+        self._gemm(B, mine)
+        if len({r for _, r in self.partition}) == 1:
             dist.all_gather_into_tensor(full, mine, group=self.group)
             return full
-        if gather == "all":
-            chunks = 1                 # unequal slabs: one grouped send/recv exchange after the GEMM
-            gather = "overlap"
-        if gather != "overlap":
-            raise ValueError(f"unknown gather mode {gather!r}")
-        # every rank must cut its slab into the same number of chunks
-        nchunks = max(1, min(chunks, min(r for _, r in self.partition) // ROW_BLOCK))
-        my_chunks = chunk_rows(self.rows, nchunks)
-        cuda = dev.type == "cuda"
-        if cuda and self._side is None:
-            self._side = torch.cuda.Stream(device=dev)
-        pending = []
-        for c, (c0, crows) in enumerate(my_chunks):
-            self._gemm(B, mine[c0:c0 + crows], c0, crows)
-            ops = []
-            for peer, (ps, prows) in enumerate(self.partition):
-                if peer == self.rank:
-                    continue
-                pc0, pcrows = chunk_rows(prows, nchunks)[c]
-                ops.append(dist.P2POp(dist.isend, mine[c0:c0 + crows], peer, group=self.group))
-                ops.append(dist.P2POp(dist.irecv, full[ps + pc0:ps + pc0 + pcrows], peer, group=self.group))
-            if cuda:
-                ready = torch.cuda.Event()
-                ready.record()
-                with torch.cuda.stream(self._side):
-                    self._side.wait_event(ready)
-                    pending += dist.batch_isend_irecv(ops)
-            else:
-                pending += dist.batch_isend_irecv(ops)
-        for w in pending:
+        # unequal slabs: every rank sends its slab to, and receives the other slabs from, every peer
+        ops = []
+        for peer, (ps, prows) in enumerate(self.partition):
+            if peer == self.rank:
+                continue
+            ops.append(dist.P2POp(dist.isend, mine, peer, group=self.group))
+            ops.append(dist.P2POp(dist.irecv, full[ps:ps + prows], peer, group=self.group))
+        for w in dist.batch_isend_irecv(ops):
             w.wait()
-        if cuda:
-            torch.cuda.current_stream().wait_stream(self._side)
         return full
 
     # -- fused GEMM + all-gather ------------------------------------------------------------------------
@@ -221,37 +184,4 @@ class ShardedBinaryLinear:
             from . import matmul_scatter
             matmul_scatter(self.packed, B, mine, extra)
         self._rank_barrier(dev)                          # every rank's stores have landed
-        return full
-
-    def _forward_push(self, B, out_dtype, chunks):
-        if out_dtype != torch.float16:
-            raise ValueError("gather='push' produces float16")
-        n, dev = B.shape[1], B.device
-        if n not in self._fused:
-            self._fused[n] = self._peer_mapped_buffer(n, dev)
-        full, _, (_, views) = self._fused[n]
-        mine = full[self.start:self.start + self.rows]
-        peers = [p for p in range(self.world) if p != self.rank]
-        cuda = dev.type == "cuda"
-        if cuda and self._push_streams is None:
-            self._push_streams = [torch.cuda.Stream(device=dev) for _ in peers]
-        self._rank_barrier(dev)                          # every rank is done reading the previous result
-        main = torch.cuda.current_stream(dev) if cuda else None
-        for c0, crows in chunk_rows(self.rows, chunks):
-            self._gemm(B, mine[c0:c0 + crows], c0, crows)
-            r0 = self.start + c0
-            if not cuda:
-                for p in peers:
-                    views[p][r0:r0 + crows].copy_(mine[c0:c0 + crows])
-                continue
-            ready = torch.cuda.Event()
-            ready.record(main)
-            for st, p in zip(self._push_streams, peers):
-                st.wait_event(ready)
-                with torch.cuda.stream(st):
-                    views[p][r0:r0 + crows].copy_(mine[c0:c0 + crows], non_blocking=True)
-        if cuda:
-            for st in self._push_streams:
-                main.wait_stream(st)
-        self._rank_barrier(dev)                          # every rank's copies have landed
         return full

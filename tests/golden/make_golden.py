@@ -52,7 +52,9 @@ def bits16(t):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path of the reference checkout>")
+    ref = load_reference(sys.argv[1])
     rng = np.random.default_rng(3080)
     out = {}
 

@@ -135,6 +135,68 @@ def test_stateless_entry_point_dispatch(lib, n, dialect):
     assert (out.cpu().numpy() == want32).all()
 
 
+def test_two_streams_share_the_library_scratch(lib):
+    # workspace == NULL on two non-blocking streams with different weights: the library orders the two calls'
+    # use of its one scratch block on the GPU, so both results are exact
+    m, n, k = 1024, 64, 2048
+    probs = [Problem(500 + i, m, k) for i in range(2)]
+    Bs = [helpers.make_tokens(p.rng, k, n, "int") for p in probs]
+    wants = [p.oracle(B, use_scale=False)[0] for p, B in zip(probs, Bs)]
+    d_bs = [dev(B) for B in Bs]
+    outs = [torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda") for _ in probs]
+    streams = [torch.cuda.Stream() for _ in probs]
+    torch.cuda.synchronize()
+    for rep in range(3):
+        for p, d_b, out, st in zip(probs, d_bs, outs, streams):
+            _lib.check(lib.onebit_sparse_matmul_ex(p.d_bits.data_ptr(), d_b.data_ptr(), out.data_ptr(), p.d_meta.data_ptr(), None,
+                                                   m, n, k, _lib.OUT_F32, p.dialect, None, 0, st.cuda_stream))
+    torch.cuda.synchronize()
+    _lib.check(lib.onebit_check_device_status())
+    for out, want in zip(outs, wants):
+        assert (out.cpu().numpy() == want).all()
+
+
+def test_single_token_from_an_unaligned_address(lib):
+    # B (k, 1) that starts 2 bytes into a buffer is legal fp16: the kernel must not use 16-byte loads on it
+    m, k = 256, 512
+    p = Problem(41, m, k)
+    B = helpers.make_tokens(p.rng, k, 1, "int")
+    want32, _ = p.oracle(B, use_scale=False)
+    buf = torch.zeros(k + 8, dtype=torch.float16, device="cuda")
+    buf[1:k + 1] = dev(B).reshape(-1)
+    out = torch.full((m, 1), float("nan"), dtype=torch.float32, device="cuda")
+    _lib.check(lib.onebit_matmul_packed(p.d_bits_tile.data_ptr(), p.d_meta_tile.data_ptr(), None, buf.data_ptr() + 2,
+                                        out.data_ptr(), m, 1, k, _lib.OUT_F32, _lib.KERNEL_DECODE, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want32).all()
+
+
+def test_weights_written_right_before_the_few_token_kernel(lib):
+    # the producer of the packed weights sits directly before the GEMM in the stream; without the
+    # stable-weights flag the kernel must not request them before that producer has completed
+    m, k, n = 4096, 4096, 4
+    p = Problem(43, m, k)
+    B = helpers.make_tokens(p.rng, k, n, "int")
+    want32, _ = p.oracle(B, use_scale=False)
+    d_b = dev(B)
+    bits_tile = torch.zeros(m * k // 16, dtype=torch.uint8, device="cuda")
+    meta_tile = torch.zeros(m * k // 8, dtype=torch.uint8, device="cuda")
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    for rep in range(5):
+        bits_tile.zero_(); meta_tile.zero_()
+        _lib.check(lib.onebit_relayout(p.d_bits.data_ptr(), p.d_meta.data_ptr(), p.dialect, m, k, bits_tile.data_ptr(),
+                                       meta_tile.data_ptr(), None))
+        _lib.check(lib.onebit_matmul_packed(bits_tile.data_ptr(), meta_tile.data_ptr(), None, d_b.data_ptr(), out.data_ptr(),
+                                            m, n, k, _lib.OUT_F32, _lib.KERNEL_DECODE, None))
+        assert (out.cpu().numpy() == want32).all()
+    # with the flag, on weights that are old by then: same result
+    _lib.check(lib.onebit_matmul_packed(bits_tile.data_ptr(), meta_tile.data_ptr(), None, d_b.data_ptr(), out.data_ptr(),
+                                        m, n, k, _lib.OUT_F32, _lib.KERNEL_DECODE | _lib.KERNEL_STABLE_WEIGHTS, None))
+    _lib.check(lib.onebit_check_device_status())
+    assert (out.cpu().numpy() == want32).all()
+
+
 def test_reference_entry_point(lib):
     # the reference's own symbol: CUTLASS-ordered metadata, fp32 D, c ignored, default stream
     m, n, k = 256, 64, 256
@@ -200,7 +262,8 @@ def _gpu_weights(m, k, seed):
     return w.reshape(m, k), scale
 
 
-@pytest.mark.parametrize("m,n,k", [(8192, 8192, 8192), (28672, 2048, 8192), (8192, 2048, 28672), (25600, 25600, 25600)])
+@pytest.mark.parametrize("m,n,k", [(4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (28672, 2048, 8192),
+                                   (8192, 2048, 28672), (25600, 25600, 25600), (65536, 8192, 8192)])
 def test_full_size_sampled_rows_and_linearity(lib, m, n, k):
     import onebitsparsemul_b200 as ob
     w, scale = _gpu_weights(m, k, seed=m + k)

@@ -16,7 +16,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle
-from onebitsparsemul_b200.sharded import ShardedBinaryLinear, chunk_rows, row_partition
+from onebitsparsemul_b200.sharded import ShardedBinaryLinear, row_partition
 from tests import helpers
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -35,8 +35,6 @@ def test_row_partition():
         row_partition(1000, 2)
     with pytest.raises(ValueError):
         row_partition(256, 2)
-    assert chunk_rows(1024, 4) == [(0, 256), (256, 256), (512, 256), (768, 256)]
-    assert chunk_rows(512, 4) == [(0, 256), (256, 256)]
 
 
 def test_slab_pack_equals_rows_of_the_canonical_pack():
@@ -99,14 +97,14 @@ def _cpu_worker(rank, world, port, mode, q, shared_dir):
         layer.pack_full(torch.from_numpy(dense), torch.from_numpy(scale))
         canon, signs, _ = oracle.compress(dense)
         want, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, 0), 0, B, m, scale=scale)
-        if mode in ("fused", "push"):
+        if mode == "fused":
             ok = True
             for _ in range(2):                              # twice: the cached buffer is reused
-                got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float16, chunks=2).numpy()
+                got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float16).numpy()
                 ok &= bool((got == want.astype(np.float16)).all())
             q.put((rank, ok, got.shape))
             return
-        got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float32, chunks=2).numpy()
+        got = layer.forward(torch.from_numpy(B), gather=mode, out_dtype=torch.float32).numpy()
         if mode == "none":
             want = want[layer.start:layer.start + layer.rows]
         q.put((rank, bool((got == want).all()), got.shape))
@@ -114,7 +112,7 @@ def _cpu_worker(rank, world, port, mode, q, shared_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["none", "all", "overlap", "fused", "push"])
+@pytest.mark.parametrize("mode", ["none", "all", "fused"])
 def test_sharded_host_logic_two_cpu_ranks(mode, tmp_path):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -155,7 +153,7 @@ def _gpu_worker(rank, world, port, q):
             slab = layer.forward(B, gather="none")
             if not bool((slab == want[layer.start:layer.start + layer.rows]).all()):
                 ok.append((n, "none"))
-            for mode in ("all", "overlap", "fused", "fused", "push", "push"):   # twice: the cached peer-mapped buffer is reused
+            for mode in ("all", "fused", "fused"):   # twice: the cached peer-mapped buffer is reused
                 if not bool((layer.forward(B, gather=mode) == want).all()):
                     ok.append((n, mode))
         ok = (ok == [], ok, layer.fused_backend)
@@ -177,7 +175,7 @@ def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
         layer = ShardedBinaryLinear(512, 256).pack_full(w)
         B = torch.from_numpy(helpers.make_tokens(rng, 256, 32)).cuda()
         want = ob.matmul_packed(ob.pack_weight(w), B, out_dtype=torch.float16)
-        for mode in ("none", "all", "overlap", "fused", "push"):
+        for mode in ("none", "all", "fused"):
             assert (layer.forward(B, gather=mode) == want).all()
         return
     ctx = mp.get_context("spawn")
