@@ -10,6 +10,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/onebit_sparse_tensor.h"
@@ -94,6 +95,13 @@ int grow_scratch_locked(DeviceScratch& s, size_t bytes) {
   return ONEBIT_OK;
 }
 
+// Which few-token kernel serves ONEBIT_KERNEL_DECODE: the tensor-memory form (default) or, with
+// ONEBIT_DECODE_VARIANT=1 in the environment, the warp-level mma.sp form it replaced (kept for comparison).
+bool use_legacy_decode() {
+  static const bool legacy = [] { const char* v = getenv("ONEBIT_DECODE_VARIANT"); return v && atoi(v) == 1; }();
+  return legacy;
+}
+
 int check_dialect_rows(int dialect, int64_t m) {
   if (dialect != OB_META_PYTHON && dialect != OB_META_CUTLASS) return fail(ONEBIT_ERR_ARG, "unknown metadata order %d", dialect);
   if (m % ob_meta_row_granule(dialect) != 0)
@@ -124,7 +132,8 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
     e = ob::launch_gemm_prefill(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, status, stream);
     if (e != cudaSuccess) return cuda_fail(e, "tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, fresh_weights, stream);
+    e = use_legacy_decode() ? ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, fresh_weights, stream)
+                            : ob::launch_gemm_fewtok(bits_tile, meta_tile, scale, nullptr, b, d, m, n, k, out_type, false, fresh_weights, stream);
     if (e != cudaSuccess) return cuda_fail(e, "decode GEMM launch");
   } else {
     return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
@@ -194,7 +203,8 @@ int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const voi
     e = ob::launch_gemm_prefill_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, status, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, fresh_weights, st);
+    e = use_legacy_decode() ? ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, fresh_weights, st)
+                            : ob::launch_gemm_fewtok(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, true, fresh_weights, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major decode GEMM launch");
   } else {
     return fail(ONEBIT_ERR_ARG, "unknown kernel selector %d", kernel);
@@ -319,6 +329,9 @@ int onebit_check_device_status(void) {
   e = ob::read_decode_status(&host);
   if (e != cudaSuccess) return cuda_fail(e, "read_decode_status");
   if (host != 0) return fail(ONEBIT_ERR_DEVICE_WAIT, "a bounded wait inside the decode kernel gave up (code %d)", host);
+  e = ob::read_fewtok_status(&host);
+  if (e != cudaSuccess) return cuda_fail(e, "read_fewtok_status");
+  if (host != 0) return fail(ONEBIT_ERR_DEVICE_WAIT, "a bounded wait inside the few-token kernel gave up (code %d)", host);
   return ONEBIT_OK;
 }
 

@@ -1,0 +1,474 @@
+// K3, tensor-memory form: the few-token kernel (n <= 16 per pass) on the 5th-generation tensor cores.
+//
+// Same job and same cluster split-K scheme as gemm_decode.cu -- stream the 1.5 bit/weight operand from HBM
+// exactly once; a cluster of S CTAs cuts K into S slices; partial sums meet in the row owner's shared memory
+// and are added in a fixed order -- but the multiply itself is the tcgen05 pipeline of the large-shape
+// kernels, shrunk to a 128 x 16 accumulator:
+//   * one CTA = one 128-row block of A x one slice of K. Weights arrive by bulk async copies in rounds of
+//     4 tiles (12 KiB) into a shared-memory ring, the whole first ring requested by one thread at kernel
+//     start;
+//   * 8 worker warps (thread = weight row, two groups of 4 warps taking alternate tiles) expand a tile's
+//     64 sign bits per row into 32 registers of fp16 +-1 pairs (one shift + one logic op per pair) and store
+//     them with tcgen05.st into a ring of tensor-memory slots; one thread copies the tile's metadata block
+//     into tensor memory (tcgen05.cp) and issues 4 x tcgen05.mma.sp.kind::f16 (M = 128, N = 16, K = 32 dense)
+//     with the +-1 operand read from tensor memory. The K loop accumulates in tensor memory, so no partial
+//     sums of a CTA ever meet in shared memory, no warp reads token fragments, and the legacy mma.sp issue
+//     cost (one instruction per 16 x 32 weights and 8 tokens) is gone;
+//   * tokens are staged by the worker warps as the B operand in the canonical no-swizzle layout: core
+//     matrices of 8 x 16 bytes. Token rows that are contiguous in k (x (n, k), or a single token) become a
+//     K-major operand; B (k, n) rows become an N-major operand, 16 bytes = 8 tokens of one k row per piece,
+//     so nothing is ever transposed element by element. Token columns beyond n are never written: what
+//     the tensor core reads there only reaches accumulator columns that are never stored;
+//   * epilogue: tcgen05.ld (thread = row, 8 token columns), then either scale and store (S = 1) or 16-byte
+//     stores into the owner CTA's shared memory, one cluster barrier, fixed-order sum, scale, store;
+//   * programmatic dependent launch as in gemm_decode.cu. Tensor memory is allocated BEFORE the CTA lets
+//     dependents start, and the kernel asks for enough shared memory that at most two CTAs share an SM: a
+//     resident CTA of the next grid can then never hold tensor memory that a CTA of this grid still needs.
+// Every mbarrier wait is bounded; a wait that gives up records a code in g_fewtok_status, and the kernel still
+// runs to its end and frees its tensor memory.
+#include <cooperative_groups.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <climits>
+#include <cstdlib>
+
+#include "formats.h"
+#include "kernels.h"
+#include "sm100_ptx.h"
+
+namespace cg = cooperative_groups;
+
+namespace {
+
+using namespace ob_ptx;
+
+#ifdef OB_TRACE
+__device__ long long g_trace_ft[4][16];
+#define OB_TRACE_EV(ev) do { if (blockIdx.x == 3 && blockIdx.z == 0 && blockIdx.y < 2 && (threadIdx.x == 0 || threadIdx.x == 288)) g_trace_ft[blockIdx.y * 2 + (threadIdx.x != 0)][ev] = clock64(); } while (0)
+#else
+#define OB_TRACE_EV(ev) do { } while (0)
+#endif
+
+// nonzero once a bounded wait has given up (200 + role code); read and cleared by the host
+__device__ int g_fewtok_status;
+
+constexpr int kTileBytes = OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
+constexpr int KL = 4;                    // tiles per round of the weight ring
+constexpr int kWorkers = 256;            // warps 0-7: tokens, expansion, epilogue
+constexpr int kThreads = kWorkers + 64;  // warp 8: weight stream, warp 9: tensor memory + MMA issue
+constexpr int kASlots = 6;               // +-1 operand slots in tensor memory (one tile each)
+constexpr int kTmemCols = 256;           // [0,16) accumulator, [32,56) metadata slots, [64,256) operand slots
+constexpr int kTmemE = 32, kTmemA = 64;
+constexpr int kMinSmem = 78 * 1024;      // at most two CTAs per SM, whatever the configuration needs
+
+// NG = groups of 8 token columns per pass (the MMA is always N = 16; with NG = 1 both halves read the same tokens)
+template <int NG> struct FewTokCfg {
+  static constexpr int NP = 8 * NG;
+  static constexpr int kRing = (NG == 1) ? 4 : 3;                             // rounds in flight
+  static constexpr int kRoundWeights = KL * kTileBytes;                       // [meta of KL tiles | signs of KL tiles]
+  static constexpr int kTileTokens = NG * 2048;                               // 128 k x 8 NG tokens, fp16
+  static constexpr int kRoundTokens = KL * kTileTokens;
+  static constexpr int kWeights = kRing * kRoundWeights;
+  static constexpr int kTokens = kRing * kRoundTokens;
+  static constexpr int kRecv = 128 * NP * 4;                                  // [source rank][row of this CTA's share][token]
+  static constexpr int kBars = 8 * (3 * kRing + 2 * kASlots + 1) + 8;         // barriers + the tensor-memory address
+  static constexpr int kNeeded = kWeights + kTokens + kRecv + kBars + 1024;   // + alignment slack
+  static constexpr int kTotal = kNeeded < kMinSmem ? kMinSmem : kNeeded;
+  static constexpr int kPieces = KL * 128 * NP / 8 / kWorkers;                // 16-byte token pieces per worker and round
+  static_assert(2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM must fit");
+  static_assert(KL * 128 * NP / 8 == kPieces * kWorkers, "a round's tokens are whole 16-byte pieces per worker");
+};
+
+struct FewTokArgs {
+  const uint8_t* bits_tile;
+  const uint8_t* meta_tile;
+  const __half* scale;
+  const __half* bias;   // per output row, added after the scale (token-major callers; NULL = none)
+  const __half* b;
+  void* d;
+  int64_t m, n, k;
+  int fresh_weights;    // 1: request no weights before the previous kernel of the stream has completed
+};
+
+__device__ __forceinline__ void tcgen05_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// TM = token-major operands (the nn.Linear convention): b is x (n, k) row-major, d is y (n, m) row-major
+template <int NG, typename OutT, bool TM>
+__global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs a) {
+  using L = FewTokCfg<NG>;
+  constexpr int NP = L::NP, kRing = L::kRing, kPieces = L::kPieces;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  OB_TRACE_EV(0);
+  // the cluster spans the whole y extent of the grid
+  const int S = (int)gridDim.y;
+  const int rank = (int)blockIdx.y;
+  const int64_t mb = blockIdx.x;
+  const int64_t n0 = (int64_t)blockIdx.z * NP;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  uint8_t* wring = smem;
+  uint8_t* tring = smem + L::kWeights;
+  float* s_recv = reinterpret_cast<float*>(smem + L::kWeights + L::kTokens);
+  const uint32_t bar0 = smem_base + L::kWeights + L::kTokens + L::kRecv;
+  auto bar_wfull = [&](int s) { return bar0 + 8 * s; };                        // a round of weights has landed
+  auto bar_wempty = [&](int s) { return bar0 + 8 * (kRing + s); };             // its MMAs are done: weights and tokens free
+  auto bar_tfull = [&](int s) { return bar0 + 8 * (2 * kRing + s); };          // its tokens are staged (8 warps)
+  auto bar_afull = [&](int x) { return bar0 + 8 * (3 * kRing + x); };          // operand slot x written (4 warps)
+  auto bar_aempty = [&](int x) { return bar0 + 8 * (3 * kRing + kASlots + x); };   // the MMAs reading slot x are done
+  const uint32_t bar_acc = bar0 + 8 * (3 * kRing + 2 * kASlots);
+  const uint32_t tmem_slot = bar_acc + 8;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - smem_base));
+
+  const int tiles_k = (int)(a.k / OB_TILE_K);
+  const int tile_begin = (int)((int64_t)tiles_k * rank / S), tile_end = (int)((int64_t)tiles_k * (rank + 1) / S);
+  const int T = tile_end - tile_begin;                        // tiles of this CTA's slice
+  const int nrounds = (T + KL - 1) / KL;
+  long long budget = 2000000000ll;
+
+  const int nvalid = (int)min((int64_t)NP, a.n - n0);
+  // token rows contiguous in k (a K-major operand): token-major callers, or a single, 16-byte aligned token
+  const bool kmajor = TM || (a.n == 1 && (reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
+  const bool vec_rows = !kmajor && (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
+  const bool quad_rows = !kmajor && (a.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 7) == 0);
+
+  if (warp == 8) {
+    // ---------------- weight stream: round r of the slice -> ring slot r % kRing ----------------
+    if (lane == 0) {
+      for (int s = 0; s < kRing; ++s) { mbar_init(bar_wfull(s), 1); mbar_init(bar_wempty(s), 1); mbar_init(bar_tfull(s), kWorkers / 32); }
+      for (int x = 0; x < kASlots; ++x) { mbar_init(bar_afull(x), 4); mbar_init(bar_aempty(x), 1); }
+      mbar_init(bar_acc, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+  } else if (warp == 9) {
+    tcgen05_alloc(tmem_slot, kTmemCols);
+    // only now may CTAs of the next grid become resident beside this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+  auto issue = [&](int r) {
+    const int s = r % kRing;
+    const int nt = min(KL, T - r * KL);
+    const int64_t tile = mb * tiles_k + tile_begin + r * KL;
+    const uint32_t dst = smem_base + s * L::kRoundWeights;
+    mbar_expect_tx(bar_wfull(s), nt * kTileBytes);
+    bulk_load(dst, a.meta_tile + tile * OB_TILE_META_BYTES, nt * OB_TILE_META_BYTES, bar_wfull(s));
+    bulk_load(dst + KL * OB_TILE_META_BYTES, a.bits_tile + tile * OB_TILE_BITS_BYTES, nt * OB_TILE_BITS_BYTES, bar_wfull(s));
+  };
+  if (warp == 8 && lane == 0) {
+    const int npre = min(nrounds, kRing);
+    for (int r = 0; r < npre; ++r) issue(r);
+  }
+  OB_TRACE_EV(1);
+
+  // tokens of one round: kPieces 16-byte pieces per worker, fetched into registers, stored as core matrices.
+  //   K-major source: piece = 8 k values of token j          -> [tile][j / 8][k chunk][j % 8]
+  //   N-major source: piece = 8 tokens (group ng) of k row kk -> [tile][ng][kk]          (16 bytes each)
+  auto fetch_tokens = [&](int r, uint4 (&tv)[kPieces]) {
+    const int ntile = min(KL, T - r * KL);
+    const int64_t k0 = (int64_t)(tile_begin + r * KL) * OB_TILE_K;
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i) {
+      tv[i] = make_uint4(0, 0, 0, 0);
+      const int idx = tid + kWorkers * i;
+      if (kmajor) {
+        const int j = idx % NP, c = idx / NP;                 // token, 8-k chunk of the round (64 chunks)
+        if (j < nvalid && (c >> 4) < ntile) tv[i] = __ldg(reinterpret_cast<const uint4*>(a.b + (n0 + j) * a.k + k0 + c * 8));
+      } else {
+        const int kk = idx / NG, ng = idx % NG;               // k row of the round, token group
+        if ((kk >> 7) < ntile && 8 * ng < nvalid) {
+          const __half* src = a.b + (k0 + kk) * a.n + n0 + 8 * ng;
+          if (vec_rows) {
+            tv[i] = __ldg(reinterpret_cast<const uint4*>(src));
+          } else if (quad_rows) {
+            uint2* h4 = reinterpret_cast<uint2*>(&tv[i]);     // n % 4 == 0: whole groups of four tokens
+            h4[0] = __ldg(reinterpret_cast<const uint2*>(src));
+            if (8 * ng + 4 < nvalid) h4[1] = __ldg(reinterpret_cast<const uint2*>(src + 4));
+          } else {
+            __half* h = reinterpret_cast<__half*>(&tv[i]);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj)
+              if (8 * ng + jj < nvalid) h[jj] = src[jj];
+          }
+        }
+      }
+    }
+  };
+  auto store_tokens = [&](int r, const uint4 (&tv)[kPieces]) {
+    const int ntile = min(KL, T - r * KL);
+    uint8_t* sb = tring + (r % kRing) * L::kRoundTokens;
+#pragma unroll
+    for (int i = 0; i < kPieces; ++i) {
+      const int idx = tid + kWorkers * i;
+      if (kmajor) {
+        const int j = idx % NP, c = idx / NP;
+        if (j < nvalid && (c >> 4) < ntile)
+          *reinterpret_cast<uint4*>(sb + (c >> 4) * L::kTileTokens + (j >> 3) * 2048 + (c & 15) * 128 + (j & 7) * 16) = tv[i];
+      } else {
+        const int kk = idx / NG, ng = idx % NG;
+        if ((kk >> 7) < ntile && 8 * ng < nvalid)
+          *reinterpret_cast<uint4*>(sb + (kk >> 7) * L::kTileTokens + ng * 2048 + (kk & 127) * 16) = tv[i];
+      }
+    }
+  };
+
+  uint4 tv[kPieces];
+  if (warp < 8) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");        // the previous kernel's results (the tokens) are complete
+    fetch_tokens(0, tv);
+  }
+  tcgen05_fence_before();
+  __syncthreads();                                            // the barriers exist, the tensor-memory address is written
+  tcgen05_fence_after();
+  // Every CTA of the cluster announces that it runs; the matching wait stands right before the first store into
+  // another CTA's shared memory, which must not be touched before that CTA has started.
+  if (S > 1) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot_gen;
+  OB_TRACE_EV(2);
+
+  if (warp < 8) {
+    // ---------------- workers: stage tokens, expand sign bits into tensor memory ----------------
+    const int q = warp & 3, grp = warp >> 2;
+    const int row = q * 32 + lane;
+#pragma unroll 1
+    for (int r = 0; r < nrounds; ++r) {
+      const int s = r % kRing;
+      if (r >= kRing) mbar_wait(bar_wempty(s), ((r / kRing) - 1) & 1, budget, &g_fewtok_status, 201);
+      store_tokens(r, tv);
+      fence_proxy_async();                                    // the tensor core reads them through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tfull(s));
+      if (r + 1 < nrounds) fetch_tokens(r + 1, tv);           // in flight while this round is expanded
+      mbar_wait(bar_wfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 202);
+      if (r == 0) OB_TRACE_EV(3);
+      const int nt = min(KL, T - r * KL);
+#pragma unroll 1
+      for (int j = grp; j < nt; j += 2) {
+        const int t = r * KL + j, x = t % kASlots;
+        mbar_wait(bar_aempty(x), ((t / kASlots) & 1) ^ 1, budget, &g_fewtok_status, 203);
+        const uint2 w = *reinterpret_cast<const uint2*>(wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + j * OB_TILE_BITS_BYTES + row * 8);
+        uint32_t v[32];
+#pragma unroll
+        for (int p = 0; p < 16; ++p) { v[p] = expand_pair(w.x, p); v[16 + p] = expand_pair(w.y, p); }
+        tcgen05_fence_after();
+        tcgen05_st_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 32 * x), v);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_afull(x));
+      }
+    }
+    OB_TRACE_EV(4);
+  } else if (warp == 8) {
+    // ---------------- weight stream: refill a slot once its round has been multiplied ----------------
+    if (lane == 0) {
+      for (int r = kRing; r < nrounds; ++r) {
+        mbar_wait(bar_wempty(r % kRing), ((r / kRing) - 1) & 1, budget, &g_fewtok_status, 204);
+        issue(r);
+      }
+    }
+  } else {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // M = 128, N = 16, sparse, fp32 accumulate; B is K-major (bit 16 clear) or N-major (bit 16 set)
+      const uint32_t idesc = (1u << 2) | (1u << 4) | (kmajor ? 0u : (1u << 16)) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      // no-swizzle core matrices: 128 bytes between 8-k groups (leading offset), 2048 between the two token groups
+      // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
+      const uint32_t sbo = (NG == 2) ? 2048u : 0u;
+      for (int r = 0; r < nrounds; ++r) {
+        const int s = r % kRing;
+        const int nt = min(KL, T - r * KL);
+        mbar_wait(bar_tfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 205);
+        mbar_wait(bar_wfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 206);
+        for (int j = 0; j < nt; ++j) {
+          const int t = r * KL + j, x = t % kASlots;
+          mbar_wait(bar_afull(x), (t / kASlots) & 1, budget, &g_fewtok_status, 207);
+          tcgen05_fence_after();
+          const uint32_t e_col = tmem_base + kTmemE + 4 * x;
+          tcgen05_cp_128x128b(e_col, make_desc(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES, 128, 128, kLayoutNone));
+          const uint32_t tok = smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens;
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb)
+            tcgen05_mma_sp_f16_ts(tmem_base, tmem_base + kTmemA + 32 * x + 8 * kb, make_desc(tok + 512 * kb, 128, sbo, kLayoutNone),
+                                  e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (t | kb) != 0);
+          tcgen05_commit(bar_aempty(x));
+        }
+        tcgen05_commit(bar_wempty(s));
+      }
+      tcgen05_commit(bar_acc);
+    }
+  }
+  __syncwarp();
+
+  // ---------------- epilogue ----------------
+  auto finish = [&](int64_t row, int j, float sum, float scale, float bias) {
+    sum = __fmul_rn(sum, scale);                              // two roundings, like the other kernels' epilogues
+    if (a.bias) sum = __fadd_rn(sum, bias);
+    if (j < nvalid) {
+      const int64_t o = TM ? (n0 + j) * a.m + row : row * a.n + n0 + j;
+      if constexpr (sizeof(OutT) == 2) static_cast<__half*>(a.d)[o] = __float2half_rn(sum);
+      else static_cast<float*>(a.d)[o] = sum;
+    }
+  };
+  const int rows_per = 128 / S;                               // S is a power of two
+  cg::cluster_group cluster = cg::this_cluster();
+  if (warp < 8) {
+    const int q = warp & 3, grp = warp >> 2;
+    if (grp < NG) {
+      const int row = q * 32 + lane;
+      mbar_wait(bar_acc, 0, budget, &g_fewtok_status, 208);
+      tcgen05_fence_after();
+      uint32_t v[8];
+      tcgen05_ld_32x32b_x8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(8 * grp), v);
+      tcgen05_fence_before();
+      OB_TRACE_EV(5);
+      if (S == 1) {
+        const int64_t grow = mb * 128 + row;
+        const float scale = a.scale ? __half2float(a.scale[grow]) : 1.f, bias = a.bias ? __half2float(a.bias[grow]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) finish(grow, 8 * grp + j, __uint_as_float(v[j]), scale, bias);
+      } else {
+        // all CTAs of the cluster have started (see the arrive above)
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        // CTA o of the cluster owns rows [o * 128/S, (o+1) * 128/S) of the block
+        float* dst = cluster.map_shared_rank(s_recv, row / rows_per) + ((rank * rows_per + row % rows_per) * NP + 8 * grp);
+        reinterpret_cast<float4*>(dst)[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
+        if (8 * grp + 4 < nvalid)
+          reinterpret_cast<float4*>(dst)[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
+      }
+    } else if (S > 1) {
+      asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    }
+  } else if (S > 1) {
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+  }
+  if (S > 1) {
+    // the per-row constants of this thread's outputs, fetched while the barrier is pending
+    constexpr int kOut = (128 * NP / 2 + kThreads - 1) / kThreads;   // outputs per thread at S = 2, the most
+    float sc[kOut], bs[kOut];
+#pragma unroll
+    for (int i = 0; i < kOut; ++i) {
+      const int e = tid + i * kThreads;
+      sc[i] = 1.f; bs[i] = 0.f;
+      if (e < rows_per * NP) {
+        const int rr = TM ? e % rows_per : e / NP;
+        const int64_t row = mb * 128 + rank * rows_per + rr;
+        if (a.scale) sc[i] = __half2float(a.scale[row]);
+        if (a.bias) bs[i] = __half2float(a.bias[row]);
+      }
+    }
+    cluster.sync();                                           // every slice's sums have arrived
+    OB_TRACE_EV(6);
+    // fixed-order sum of the S slices from this CTA's own shared memory
+#pragma unroll
+    for (int i = 0; i < kOut; ++i) {
+      const int e = tid + i * kThreads;
+      if (e < rows_per * NP) {
+        // consecutive threads walk the fastest output dimension: tokens of a row (m x n), rows of a token (n x m)
+        const int rr = TM ? e % rows_per : e / NP, j = TM ? e / rows_per : e % NP;
+        float sum = 0.f;
+        for (int sl = 0; sl < S; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
+        finish(mb * 128 + rank * rows_per + rr, j, sum, sc[i], bs[i]);
+      }
+    }
+  }
+  OB_TRACE_EV(7);
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    tcgen05_fence_after();
+    tcgen05_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int NG, typename OutT, bool TM>
+cudaError_t launch(const FewTokArgs& a, int S, cudaStream_t stream) {
+  using L = FewTokCfg<NG>;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(ob_gemm_fewtok_kernel<NG, OutT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(a.m / 128), (unsigned)S, (unsigned)((a.n + L::NP - 1) / L::NP));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)S;
+  attr[0].val.clusterDim.z = 1;
+  // let this grid start while the previous kernel of the stream drains (ONEBIT_PDL=0 turns it off)
+  static const bool pdl = [] { const char* v = getenv("ONEBIT_PDL"); return !(v && atoi(v) == 0); }();
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, ob_gemm_fewtok_kernel<NG, OutT, TM>, a);
+}
+
+// K split over a cluster of S CTAs. A CTA multiplies its slice in rounds of KL tiles, and an SM holds two
+// CTAs: S minimises rounds x CTAs per SM among the splits that keep the grid one wave.
+int pick_split(int64_t m, int64_t k) {
+  const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
+  const int sms = ob::sm_count();
+  int best = 1;
+  long long best_cost = LLONG_MAX;
+  for (int S = 1; S <= 8; S *= 2) {
+    if (S > 1 && (row_blocks * S > 2 * sms || tiles_k < S)) break;
+    const long long T = (tiles_k + S - 1) / S, rounds = (T + KL - 1) / KL, per_sm = (row_blocks * S + sms - 1) / sms;
+    if (rounds * per_sm <= best_cost) { best = S; best_cost = rounds * per_sm; }   // ties: more CTAs stream
+  }
+  static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_SPLIT"); return v ? atoi(v) : 0; }();
+  if ((forced == 1 || forced == 2 || forced == 4 || forced == 8) && forced <= tiles_k) best = forced;
+  return best;
+}
+
+template <bool TM>
+cudaError_t dispatch(const FewTokArgs& a, int out_type, cudaStream_t stream) {
+  const bool two = (a.n > 8);
+  const int S = pick_split(a.m, a.k);
+  if (out_type == OB_OUT_F16) return two ? launch<2, __half, TM>(a, S, stream) : launch<1, __half, TM>(a, S, stream);
+  return two ? launch<2, float, TM>(a, S, stream) : launch<1, float, TM>(a, S, stream);
+}
+
+}  // namespace
+
+namespace ob {
+
+cudaError_t launch_gemm_fewtok(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                               const void* b, void* d, int64_t m, int64_t n, int64_t k, int out_type, bool token_major,
+                               bool fresh_weights, cudaStream_t stream) {
+  FewTokArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
+               static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(b), d, m, n, k,
+               fresh_weights ? 1 : 0};
+  return token_major ? dispatch<true>(a, out_type, stream) : dispatch<false>(a, out_type, stream);
+}
+
+// Reads and clears this kernel's wait status on the current device (0 = no wait gave up).
+cudaError_t read_fewtok_status(int* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_fewtok_status, sizeof(int));
+  if (e != cudaSuccess || *out == 0) return e;
+  const int zero = 0;
+  return cudaMemcpyToSymbol(g_fewtok_status, &zero, sizeof(int));
+}
+
+}  // namespace ob
+
+#ifdef OB_TRACE
+extern "C" int onebit_debug_read_trace_fewtok(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace_ft, sizeof(long long) * 4 * 16);
+}
+#endif

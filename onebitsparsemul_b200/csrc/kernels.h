@@ -51,5 +51,11 @@ cudaError_t launch_gemm_decode_tokens(const void* bits_tile, const void* meta_ti
                                       bool fresh_weights, cudaStream_t stream);
 // Reads and clears the decode kernel's bounded-wait status on the current device (0 = nothing gave up).
 cudaError_t read_decode_status(int* out);
+// K3, tensor-memory form (gemm_decode_sm100.cu): the few-token kernel on tcgen05.mma.sp with a 128 x 16 accumulator.
+// Same operands as the two launchers above; token_major selects x (n, k) / y (n, m).
+cudaError_t launch_gemm_fewtok(const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                               const void* b, void* d, int64_t m, int64_t n, int64_t k, int out_type, bool token_major,
+                               bool fresh_weights, cudaStream_t stream);
+cudaError_t read_fewtok_status(int* out);
 
 }  // namespace ob
