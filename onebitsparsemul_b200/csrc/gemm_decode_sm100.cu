@@ -19,14 +19,18 @@
 //     K-major operand; B (k, n) rows become an N-major operand, 16 bytes = 8 tokens of one k row per piece,
 //     so nothing is ever transposed element by element. Token columns beyond n are never written: what
 //     the tensor core reads there only reaches accumulator columns that are never stored;
-//   * epilogue: tcgen05.ld (thread = row, 8 token columns), then either scale and store (S = 1) or 16-byte
-//     stores into the owner CTA's shared memory, one cluster barrier, fixed-order sum, scale, store;
+//   * consecutive MMAs go to four separate accumulators (one per 32-k block of a tile): a 128 x 16 MMA is a few
+//     cycles of tensor work, and a chain of dependent ones on a single accumulator ran at the pipeline's latency,
+//     ~200 cycles each; the four are added in the epilogue in a fixed order;
+//   * epilogue: tcgen05.ld (thread = row, 8 token columns per accumulator), then either scale and store (S = 1)
+//     or asynchronous 16-byte stores into the owner CTA's shared memory that complete on the owner's mbarrier
+//     (st.async): data and signal travel together, so no cluster-wide barrier and no release fence stand between
+//     the last MMA and the sum. The owner adds the S slices in a fixed order, scales, stores;
 //   * programmatic dependent launch as in gemm_decode.cu. Tensor memory is allocated BEFORE the CTA lets
 //     dependents start, and the kernel asks for enough shared memory that at most two CTAs share an SM: a
 //     resident CTA of the next grid can then never hold tensor memory that a CTA of this grid still needs.
 // Every mbarrier wait is bounded; a wait that gives up records a code in g_fewtok_status, and the kernel still
 // runs to its end and frees its tensor memory.
-#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -37,17 +41,24 @@
 #include "kernels.h"
 #include "sm100_ptx.h"
 
-namespace cg = cooperative_groups;
-
 namespace {
 
 using namespace ob_ptx;
 
+// Timeline instrumentation for tuning, compiled in only with -DOB_TRACE: one CTA records the SM clock at the
+// hand-overs of its pipeline. Row 0: events of worker thread 0, row 1: events of the MMA thread, rows 2/3: start
+// and end of each tile expansion of worker thread 0, rows 4/5: operand ready / MMAs issued per tile (MMA thread),
+// rows 6-10: after the metadata copy and after each of the four MMAs.
 #ifdef OB_TRACE
-__device__ long long g_trace_ft[4][16];
-#define OB_TRACE_EV(ev) do { if (blockIdx.x == 3 && blockIdx.z == 0 && blockIdx.y < 2 && (threadIdx.x == 0 || threadIdx.x == 288)) g_trace_ft[blockIdx.y * 2 + (threadIdx.x != 0)][ev] = clock64(); } while (0)
+__device__ long long g_trace_ft[16][64];
+#define OB_TRACE_ON (blockIdx.x == 3 && blockIdx.z == 0 && blockIdx.y == 0)
+#define OB_TRACE_EV(ev) do { if (OB_TRACE_ON && (threadIdx.x == 0 || threadIdx.x == 288)) g_trace_ft[threadIdx.x != 0][ev] = clock64(); } while (0)
+#define OB_TRACE_TILE(row, t) do { if (OB_TRACE_ON && (t) < 64 && (threadIdx.x == 0 || threadIdx.x == 128 || threadIdx.x == 288)) g_trace_ft[row][t] = clock64(); } while (0)
+#define OB_TRACE_ROUND(row, r) do { if (OB_TRACE_ON && (r) < 64 && threadIdx.x == 0) g_trace_ft[row][r] = clock64(); } while (0)
 #else
 #define OB_TRACE_EV(ev) do { } while (0)
+#define OB_TRACE_TILE(row, t) do { } while (0)
+#define OB_TRACE_ROUND(row, r) do { } while (0)
 #endif
 
 // nonzero once a bounded wait has given up (200 + role code); read and cleared by the host
@@ -57,10 +68,18 @@ constexpr int kTileBytes = OB_TILE_META_BYTES + OB_TILE_BITS_BYTES;
 constexpr int KL = 4;                    // tiles per round of the weight ring
 constexpr int kWorkers = 256;            // warps 0-7: tokens, expansion, epilogue
 constexpr int kThreads = kWorkers + 64;  // warp 8: weight stream, warp 9: tensor memory + MMA issue
-constexpr int kASlots = 6;               // +-1 operand slots in tensor memory (one tile each)
-constexpr int kTmemCols = 256;           // [0,16) accumulator, [32,56) metadata slots, [64,256) operand slots
-constexpr int kTmemE = 32, kTmemA = 64;
+constexpr int kAccs = 4;                 // independent accumulators of 16 columns (one per 32-k block of a tile)
+constexpr int kASlots = 4;               // +-1 operand slots in tensor memory (one tile each); a power of two
+constexpr int kTmemCols = 256;           // [0,64) accumulators, [64,80) metadata slots, [96,224) operand slots
+constexpr int kTmemE = 64, kTmemA = 96;
+constexpr int kPairs = kASlots / 2;      // slots are handed over in pairs of consecutive tiles: one commit per pair
+static_assert(kASlots == 4 && KL % 2 == 0, "the slot ring is indexed with masks; a round is whole pairs");
+static_assert(kTmemA + 32 * kASlots <= kTmemCols && kTmemE + 4 * kASlots <= kTmemA && 16 * kAccs <= kTmemE, "tensor memory plan");
+#ifdef OB_DBG_ONECTA
+constexpr int kMinSmem = 120 * 1024;
+#else
 constexpr int kMinSmem = 78 * 1024;      // at most two CTAs per SM, whatever the configuration needs
+#endif
 
 // NG = groups of 8 token columns per pass (the MMA is always N = 16; with NG = 1 both halves read the same tokens)
 template <int NG> struct FewTokCfg {
@@ -71,12 +90,14 @@ template <int NG> struct FewTokCfg {
   static constexpr int kRoundTokens = KL * kTileTokens;
   static constexpr int kWeights = kRing * kRoundWeights;
   static constexpr int kTokens = kRing * kRoundTokens;
-  static constexpr int kRecv = 128 * NP * 4;                                  // [source rank][row of this CTA's share][token]
-  static constexpr int kBars = 8 * (3 * kRing + 2 * kASlots + 1) + 8;         // barriers + the tensor-memory address
+  static constexpr int kRecv = 136 * NP * 4;                                  // [source rank][row of this CTA's share][token]; S x ceil(128 / S) <= 133 rows
+  static constexpr int kBars = 8 * (3 * kRing + 2 * kPairs + 2) + 8;          // barriers + the tensor-memory address
   static constexpr int kNeeded = kWeights + kTokens + kRecv + kBars + 1024;   // + alignment slack
   static constexpr int kTotal = kNeeded < kMinSmem ? kMinSmem : kNeeded;
   static constexpr int kPieces = KL * 128 * NP / 8 / kWorkers;                // 16-byte token pieces per worker and round
+#ifndef OB_DBG_ONECTA
   static_assert(2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM must fit");
+#endif
   static_assert(KL * 128 * NP / 8 == kPieces * kWorkers, "a round's tokens are whole 16-byte pieces per worker");
 };
 
@@ -91,11 +112,29 @@ struct FewTokArgs {
   int fresh_weights;    // 1: request no weights before the previous kernel of the stream has completed
 };
 
+// start-address field of a shared-memory matrix descriptor: bits 4-17 of the address. The mask matters: inside a
+// cluster the shared-window address of a CTA carries its rank in the upper bits
+__device__ __forceinline__ uint64_t desc_addr(uint32_t saddr) { return (uint64_t)((saddr >> 4) & 0x3FFFu); }
+
+// true in exactly one lane of a converged warp (the same lane every time)
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void tcgen05_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "r"(taddr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 16 bytes into the shared memory of a CTA of the cluster; the store completes on that CTA's mbarrier (16 bytes of
+// its transaction count), so the receiver learns of the data without any further synchronisation
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, float x, float y, float z, float w, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(cluster_addr), "f"(x), "f"(y), "f"(z), "f"(w), "r"(cluster_bar) : "memory");
 }
 
 // TM = token-major operands (the nn.Linear convention): b is x (n, k) row-major, d is y (n, m) row-major
@@ -122,10 +161,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   auto bar_wfull = [&](int s) { return bar0 + 8 * s; };                        // a round of weights has landed
   auto bar_wempty = [&](int s) { return bar0 + 8 * (kRing + s); };             // its MMAs are done: weights and tokens free
   auto bar_tfull = [&](int s) { return bar0 + 8 * (2 * kRing + s); };          // its tokens are staged (8 warps)
-  auto bar_afull = [&](int x) { return bar0 + 8 * (3 * kRing + x); };          // operand slot x written (4 warps)
-  auto bar_aempty = [&](int x) { return bar0 + 8 * (3 * kRing + kASlots + x); };   // the MMAs reading slot x are done
-  const uint32_t bar_acc = bar0 + 8 * (3 * kRing + 2 * kASlots);
-  const uint32_t tmem_slot = bar_acc + 8;
+  auto bar_afull = [&](int y) { return bar0 + 8 * (3 * kRing + y); };          // both operand slots of pair y written (8 warps)
+  auto bar_aempty = [&](int y) { return bar0 + 8 * (3 * kRing + kPairs + y); };    // the MMAs reading pair y are done
+  const uint32_t bar_acc = bar0 + 8 * (3 * kRing + 2 * kPairs);
+  const uint32_t bar_recv = bar_acc + 8;                                       // every slice's sums for this CTA's rows have landed
+  const uint32_t tmem_slot = bar_recv + 8;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - smem_base));
 
   const int tiles_k = (int)(a.k / OB_TILE_K);
@@ -133,27 +173,18 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   const int T = tile_end - tile_begin;                        // tiles of this CTA's slice
   const int nrounds = (T + KL - 1) / KL;
   long long budget = 2000000000ll;
-
   const int nvalid = (int)min((int64_t)NP, a.n - n0);
+
   // token rows contiguous in k (a K-major operand): token-major callers, or a single, 16-byte aligned token
   const bool kmajor = TM || (a.n == 1 && (reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
   const bool vec_rows = !kmajor && (a.n % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 15) == 0);
   const bool quad_rows = !kmajor && (a.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.b) & 7) == 0);
 
-  if (warp == 8) {
-    // ---------------- weight stream: round r of the slice -> ring slot r % kRing ----------------
-    if (lane == 0) {
-      for (int s = 0; s < kRing; ++s) { mbar_init(bar_wfull(s), 1); mbar_init(bar_wempty(s), 1); mbar_init(bar_tfull(s), kWorkers / 32); }
-      for (int x = 0; x < kASlots; ++x) { mbar_init(bar_afull(x), 4); mbar_init(bar_aempty(x), 1); }
-      mbar_init(bar_acc, 1);
-      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
-    }
-  } else if (warp == 9) {
-    tcgen05_alloc(tmem_slot, kTmemCols);
-    // only now may CTAs of the next grid become resident beside this one
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  }
+  // split-K hand-off: CTA o of the cluster owns rows [o * rows_per, (o+1) * rows_per) of the block and receives,
+  // from every CTA of the cluster (itself included), 16-byte pieces of those rows' sums
+  const int rows_per = (128 + S - 1) / S;
+  const int rows_owned = max(0, min(rows_per, 128 - rank * rows_per));
+  const int npieces = (nvalid + 3) / 4;                       // 16-byte pieces per row and sender
   auto issue = [&](int r) {
     const int s = r % kRing;
     const int nt = min(KL, T - r * KL);
@@ -163,9 +194,26 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     bulk_load(dst, a.meta_tile + tile * OB_TILE_META_BYTES, nt * OB_TILE_META_BYTES, bar_wfull(s));
     bulk_load(dst + KL * OB_TILE_META_BYTES, a.bits_tile + tile * OB_TILE_BITS_BYTES, nt * OB_TILE_BITS_BYTES, bar_wfull(s));
   };
-  if (warp == 8 && lane == 0) {
-    const int npre = min(nrounds, kRing);
-    for (int r = 0; r < npre; ++r) issue(r);
+  if (warp == 8) {
+    // ---------------- weight stream: round r of the slice -> ring slot r % kRing ----------------
+    if (lane == 0) {
+      // the barriers of the weight ring first, so that the first ring of loads is out as early as possible
+      for (int s = 0; s < kRing; ++s) mbar_init(bar_wfull(s), 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
+      const int npre = min(nrounds, kRing);
+      for (int r = 0; r < npre; ++r) issue(r);
+      for (int s = 0; s < kRing; ++s) { mbar_init(bar_wempty(s), 1); mbar_init(bar_tfull(s), kWorkers / 32); }
+      for (int y = 0; y < kPairs; ++y) { mbar_init(bar_afull(y), kWorkers / 32); mbar_init(bar_aempty(y), 1); }
+      mbar_init(bar_acc, 1);
+      mbar_init(bar_recv, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      if (S > 1) mbar_expect_tx(bar_recv, (uint32_t)(S * rows_owned * npieces * 16));
+    }
+  } else if (warp == 9) {
+    tcgen05_alloc(tmem_slot, kTmemCols);
+    // only now may CTAs of the next grid become resident beside this one
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
   OB_TRACE_EV(1);
 
@@ -234,6 +282,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   const uint32_t tmem_base = *tmem_slot_gen;
   OB_TRACE_EV(2);
 
+#ifdef OB_DBG_LANE0POLL
+#define WORKER_WAIT(bar, par, code) do { if (lane == 0) mbar_wait(bar, par, budget, &g_fewtok_status, code); __syncwarp(); } while (0)
+#else
+#define WORKER_WAIT(bar, par, code) mbar_wait(bar, par, budget, &g_fewtok_status, code)
+#endif
   if (warp < 8) {
     // ---------------- workers: stage tokens, expand sign bits into tensor memory ----------------
     const int q = warp & 3, grp = warp >> 2;
@@ -241,28 +294,39 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
 #pragma unroll 1
     for (int r = 0; r < nrounds; ++r) {
       const int s = r % kRing;
-      if (r >= kRing) mbar_wait(bar_wempty(s), ((r / kRing) - 1) & 1, budget, &g_fewtok_status, 201);
+      OB_TRACE_ROUND(12, r);
+      if (r >= kRing) WORKER_WAIT(bar_wempty(s), ((r / kRing) - 1) & 1, 201);
+      OB_TRACE_ROUND(13, r);
       store_tokens(r, tv);
       fence_proxy_async();                                    // the tensor core reads them through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tfull(s));
+      OB_TRACE_ROUND(14, r);
       if (r + 1 < nrounds) fetch_tokens(r + 1, tv);           // in flight while this round is expanded
-      mbar_wait(bar_wfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 202);
+      WORKER_WAIT(bar_wfull(s), (r / kRing) & 1, 202);
+      OB_TRACE_ROUND(15, r);
       if (r == 0) OB_TRACE_EV(3);
       const int nt = min(KL, T - r * KL);
 #pragma unroll 1
-      for (int j = grp; j < nt; j += 2) {
-        const int t = r * KL + j, x = t % kASlots;
-        mbar_wait(bar_aempty(x), ((t / kASlots) & 1) ^ 1, budget, &g_fewtok_status, 203);
-        const uint2 w = *reinterpret_cast<const uint2*>(wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + j * OB_TILE_BITS_BYTES + row * 8);
-        uint32_t v[32];
+      for (int pp = 0; 2 * pp < nt; ++pp) {
+        // pair P of the slice = tiles 2P (first group of warps) and 2P + 1 (second group); its two operand slots
+        // are handed back by one commit and handed over by one barrier
+        const int P = r * (KL / 2) + pp, y = P & 1, j = 2 * pp + grp;
+        if (j < nt) {
+          const int t = r * KL + j, x = t & (kASlots - 1);
+          WORKER_WAIT(bar_aempty(y), ((P >> 1) & 1) ^ 1, 203);
+          OB_TRACE_TILE(2, t);
+          const uint2 w = *reinterpret_cast<const uint2*>(wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + j * OB_TILE_BITS_BYTES + row * 8);
+          uint32_t v[32];
 #pragma unroll
-        for (int p = 0; p < 16; ++p) { v[p] = expand_pair(w.x, p); v[16 + p] = expand_pair(w.y, p); }
-        tcgen05_fence_after();
-        tcgen05_st_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 32 * x), v);
-        tcgen05_fence_before();
+          for (int p = 0; p < 16; ++p) { v[p] = expand_pair(w.x, p); v[16 + p] = expand_pair(w.y, p); }
+          tcgen05_fence_after();
+          tcgen05_st_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 32 * x), v);
+          tcgen05_fence_before();
+          OB_TRACE_TILE(3, t);
+        }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_afull(x));
+        if (lane == 0) mbar_arrive(bar_afull(y));             // also for a missing second tile: the count is 8 warps
       }
     }
     OB_TRACE_EV(4);
@@ -276,34 +340,58 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     }
   } else {
     // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      // M = 128, N = 16, sparse, fp32 accumulate; B is K-major (bit 16 clear) or N-major (bit 16 set)
-      const uint32_t idesc = (1u << 2) | (1u << 4) | (kmajor ? 0u : (1u << 16)) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      // no-swizzle core matrices: 128 bytes between 8-k groups (leading offset), 2048 between the two token groups
-      // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
-      const uint32_t sbo = (NG == 2) ? 2048u : 0u;
-      for (int r = 0; r < nrounds; ++r) {
-        const int s = r % kRing;
-        const int nt = min(KL, T - r * KL);
-        mbar_wait(bar_tfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 205);
-        mbar_wait(bar_wfull(s), (r / kRing) & 1, budget, &g_fewtok_status, 206);
-        for (int j = 0; j < nt; ++j) {
-          const int t = r * KL + j, x = t % kASlots;
-          mbar_wait(bar_afull(x), (t / kASlots) & 1, budget, &g_fewtok_status, 207);
+    // The whole warp walks the loop and one elected lane does the work of an iteration inside a single
+    // elect.sync block: wait for the tile's operand, copy its metadata, issue its four MMAs, commit. Under the
+    // elect predicate the operands of the tcgen05 instructions (descriptors, tensor-memory addresses) are
+    // warp-uniform values; issued from a branch on the lane number every instruction cost 60-75 cycles, and with
+    // all 32 lanes polling the barrier and a warp barrier per tile an iteration took 650 cycles.
+    // M = 128, N = 16, sparse, fp32 accumulate; B is K-major (bit 16 clear) or N-major (bit 16 set)
+    const uint32_t idesc = (1u << 2) | (1u << 4) | (kmajor ? 0u : (1u << 16)) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    // no-swizzle core matrices: 128 bytes between 8-k groups (leading offset), 2048 between the two token groups
+    // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
+    const uint64_t tok_desc = make_desc(0, 128, (NG == 2) ? 2048u : 0u, kLayoutNone);
+    const uint64_t meta_desc = make_desc(0, 128, 128, kLayoutNone);
+    int s = 0, rph = 0;                                       // ring slot and phase of the round
+#pragma unroll 1
+    for (int r = 0; r < nrounds; ++r) {
+      const int nt = min(KL, T - r * KL);
+#pragma unroll 1
+      for (int pp = 0; 2 * pp < nt; ++pp) {
+        const int P = r * (KL / 2) + pp, y = P & 1;
+        OB_TRACE_TILE(11, 2 * P);
+        if (elect_one()) {
+          if (pp == 0) {
+            mbar_wait(bar_tfull(s), rph, budget, &g_fewtok_status, 205);
+            mbar_wait(bar_wfull(s), rph, budget, &g_fewtok_status, 206);
+          }
+          mbar_wait(bar_afull(y), (P >> 1) & 1, budget, &g_fewtok_status, 207);
+          OB_TRACE_TILE(4, 2 * P);
           tcgen05_fence_after();
-          const uint32_t e_col = tmem_base + kTmemE + 4 * x;
-          tcgen05_cp_128x128b(e_col, make_desc(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES, 128, 128, kLayoutNone));
-          const uint32_t tok = smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens;
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb)
-            tcgen05_mma_sp_f16_ts(tmem_base, tmem_base + kTmemA + 32 * x + 8 * kb, make_desc(tok + 512 * kb, 128, sbo, kLayoutNone),
-                                  e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), (t | kb) != 0);
-          tcgen05_commit(bar_aempty(x));
+          for (int h = 0; h < 2; ++h) {
+            const int j = 2 * pp + h;
+            if (j < nt) {
+              const int t = r * KL + j, x = t & (kASlots - 1);
+              const uint32_t e_col = tmem_base + kTmemE + 4 * x;
+              tcgen05_cp_128x128b(e_col, meta_desc | desc_addr(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES));
+              OB_TRACE_TILE(6, t);
+              const uint64_t tok = tok_desc | desc_addr(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens);
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb) {
+                tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * x + 8 * kb, tok + (uint64_t)(32 * kb),
+                                      e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
+                OB_TRACE_TILE(7 + kb, t);
+              }
+            }
+          }
+          tcgen05_commit(bar_aempty(y));
+          if (2 * pp + 2 >= nt) tcgen05_commit(bar_wempty(s));   // the round's weights and tokens are free again
+          OB_TRACE_TILE(5, 2 * P);
         }
-        tcgen05_commit(bar_wempty(s));
       }
-      tcgen05_commit(bar_acc);
+      if (++s == kRing) { s = 0; rph ^= 1; }
     }
+    if (elect_one()) tcgen05_commit(bar_acc);
   }
   __syncwarp();
 
@@ -317,31 +405,37 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       else static_cast<float*>(a.d)[o] = sum;
     }
   };
-  const int rows_per = 128 / S;                               // S is a power of two
-  cg::cluster_group cluster = cg::this_cluster();
   if (warp < 8) {
     const int q = warp & 3, grp = warp >> 2;
     if (grp < NG) {
       const int row = q * 32 + lane;
       mbar_wait(bar_acc, 0, budget, &g_fewtok_status, 208);
       tcgen05_fence_after();
-      uint32_t v[8];
-      tcgen05_ld_32x32b_x8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(8 * grp), v);
+      // the four accumulators, added in a fixed order
+      float v[8];
+      {
+        uint32_t u[kAccs][8];
+#pragma unroll
+        for (int c = 0; c < kAccs; ++c) tcgen05_ld_32x32b_x8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(16 * c + 8 * grp), u[c]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (__uint_as_float(u[0][j]) + __uint_as_float(u[1][j])) + (__uint_as_float(u[2][j]) + __uint_as_float(u[3][j]));
+      }
       tcgen05_fence_before();
       OB_TRACE_EV(5);
       if (S == 1) {
         const int64_t grow = mb * 128 + row;
         const float scale = a.scale ? __half2float(a.scale[grow]) : 1.f, bias = a.bias ? __half2float(a.bias[grow]) : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) finish(grow, 8 * grp + j, __uint_as_float(v[j]), scale, bias);
+        for (int j = 0; j < 8; ++j) finish(grow, 8 * grp + j, v[j], scale, bias);
       } else {
-        // all CTAs of the cluster have started (see the arrive above)
+        // all CTAs of the cluster have started and initialised their barriers (see the arrive above)
         asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
-        // CTA o of the cluster owns rows [o * 128/S, (o+1) * 128/S) of the block
-        float* dst = cluster.map_shared_rank(s_recv, row / rows_per) + ((rank * rows_per + row % rows_per) * NP + 8 * grp);
-        reinterpret_cast<float4*>(dst)[0] = make_float4(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]), __uint_as_float(v[3]));
-        if (8 * grp + 4 < nvalid)
-          reinterpret_cast<float4*>(dst)[1] = make_float4(__uint_as_float(v[4]), __uint_as_float(v[5]), __uint_as_float(v[6]), __uint_as_float(v[7]));
+        const uint32_t owner = (uint32_t)(row / rows_per);
+        const uint32_t local = smem_base + L::kWeights + L::kTokens + (uint32_t)(((rank * rows_per + row % rows_per) * NP + 8 * grp) * 4);
+        const uint32_t dst = map_to_cta(local, owner), dbar = map_to_cta(bar_recv, owner);
+        if (8 * grp < nvalid) st_async_v4(dst, v[0], v[1], v[2], v[3], dbar);
+        if (8 * grp + 4 < nvalid) st_async_v4(dst + 16, v[4], v[5], v[6], v[7], dbar);
       }
     } else if (S > 1) {
       asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
@@ -350,32 +444,34 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
   }
   if (S > 1) {
-    // the per-row constants of this thread's outputs, fetched while the barrier is pending
+    // the per-row constants of this thread's outputs, fetched while the sums travel
     constexpr int kOut = (128 * NP / 2 + kThreads - 1) / kThreads;   // outputs per thread at S = 2, the most
     float sc[kOut], bs[kOut];
 #pragma unroll
     for (int i = 0; i < kOut; ++i) {
       const int e = tid + i * kThreads;
       sc[i] = 1.f; bs[i] = 0.f;
-      if (e < rows_per * NP) {
-        const int rr = TM ? e % rows_per : e / NP;
+      if (e < rows_owned * NP) {
+        const int rr = TM ? e % rows_owned : e / NP;
         const int64_t row = mb * 128 + rank * rows_per + rr;
         if (a.scale) sc[i] = __half2float(a.scale[row]);
         if (a.bias) bs[i] = __half2float(a.bias[row]);
       }
     }
-    cluster.sync();                                           // every slice's sums have arrived
+    mbar_wait(bar_recv, 0, budget, &g_fewtok_status, 209);    // every slice's sums for this CTA's rows have landed
     OB_TRACE_EV(6);
     // fixed-order sum of the S slices from this CTA's own shared memory
 #pragma unroll
     for (int i = 0; i < kOut; ++i) {
       const int e = tid + i * kThreads;
-      if (e < rows_per * NP) {
+      if (e < rows_owned * NP) {
         // consecutive threads walk the fastest output dimension: tokens of a row (m x n), rows of a token (n x m)
-        const int rr = TM ? e % rows_per : e / NP, j = TM ? e / rows_per : e % NP;
-        float sum = 0.f;
-        for (int sl = 0; sl < S; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
-        finish(mb * 128 + rank * rows_per + rr, j, sum, sc[i], bs[i]);
+        const int rr = TM ? e % rows_owned : e / NP, j = TM ? e / rows_owned : e % NP;
+        if (j < nvalid) {
+          float sum = 0.f;
+          for (int sl = 0; sl < S; ++sl) sum += s_recv[(sl * rows_per + rr) * NP + j];
+          finish(mb * 128 + rank * rows_per + rr, j, sum, sc[i], bs[i]);
+        }
       }
     }
   }
@@ -419,20 +515,24 @@ cudaError_t launch(const FewTokArgs& a, int S, cudaStream_t stream) {
   return cudaLaunchKernelEx(&cfg, ob_gemm_fewtok_kernel<NG, OutT, TM>, a);
 }
 
-// K split over a cluster of S CTAs. A CTA multiplies its slice in rounds of KL tiles, and an SM holds two
-// CTAs: S minimises rounds x CTAs per SM among the splits that keep the grid one wave.
+// K split over a cluster of S CTAs (1..8; the slices need not be equal). Two CTAs share an SM, so a wave holds
+// 2 x SMs CTAs; a CTA costs a fixed start-up (allocation, barriers, one DRAM round trip) plus its tiles, and a
+// split costs the hand-off of the partial sums. S minimises waves x (start-up + tiles) + hand-off in that model,
+// whose constants are cycles measured with the kernel's own timeline.
 int pick_split(int64_t m, int64_t k) {
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
-  const int sms = ob::sm_count();
+  const long long wave = 2ll * ob::sm_count();
+  constexpr long long kStart = 2500, kTile = 270, kHandOff = 800;
   int best = 1;
   long long best_cost = LLONG_MAX;
-  for (int S = 1; S <= 8; S *= 2) {
-    if (S > 1 && (row_blocks * S > 2 * sms || tiles_k < S)) break;
-    const long long T = (tiles_k + S - 1) / S, rounds = (T + KL - 1) / KL, per_sm = (row_blocks * S + sms - 1) / sms;
-    if (rounds * per_sm <= best_cost) { best = S; best_cost = rounds * per_sm; }   // ties: more CTAs stream
+  for (int S = 1; S <= 8; ++S) {
+    if (tiles_k < S) break;
+    const long long ctas = row_blocks * S, waves = (ctas + wave - 1) / wave, T = (tiles_k + S - 1) / S;
+    const long long cost = waves * (kStart + T * kTile) + (S > 1 ? kHandOff : 0);
+    if (cost < best_cost) { best = S; best_cost = cost; }
   }
   static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_SPLIT"); return v ? atoi(v) : 0; }();
-  if ((forced == 1 || forced == 2 || forced == 4 || forced == 8) && forced <= tiles_k) best = forced;
+  if (forced >= 1 && forced <= 8 && forced <= tiles_k) best = forced;
   return best;
 }
 
@@ -469,6 +569,6 @@ cudaError_t read_fewtok_status(int* out) {
 
 #ifdef OB_TRACE
 extern "C" int onebit_debug_read_trace_fewtok(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_trace_ft, sizeof(long long) * 4 * 16);
+  return (int)cudaMemcpyFromSymbol(host_out, g_trace_ft, sizeof(long long) * 16 * 64);
 }
 #endif

@@ -455,7 +455,7 @@ print("decode ring ok")
 """
 
 
-@pytest.mark.parametrize("split", ["1", "2"])
+@pytest.mark.parametrize("split", ["1", "2", "3", "5", "7", "8"])
 def test_decode_kernel_long_slices_exact(split):
     import os
     import subprocess
