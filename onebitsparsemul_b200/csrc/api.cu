@@ -95,11 +95,17 @@ int grow_scratch_locked(DeviceScratch& s, size_t bytes) {
   return ONEBIT_OK;
 }
 
-// Which few-token kernel serves ONEBIT_KERNEL_DECODE: the tensor-memory form (default) or, with
-// ONEBIT_DECODE_VARIANT=1 in the environment, the warp-level mma.sp form it replaced (kept for comparison).
-bool use_legacy_decode() {
-  static const bool legacy = [] { const char* v = getenv("ONEBIT_DECODE_VARIANT"); return v && atoi(v) == 1; }();
-  return legacy;
+// Which few-token kernel serves ONEBIT_KERNEL_DECODE. Both stream the same tile-ordered operands with the same
+// cluster split-K; the tensor-memory form (gemm_decode_sm100.cu) is faster except for the smallest calls, where
+// its longer start-up (tensor-memory allocation, more hand-overs before the first MMA) outweighs its cheaper
+// multiply phase: measured 4.9 against 4.3 us at 4096 x 4096 with up to 8 tokens, 7.6 against 8.5 us at
+// 11008 x 4096, 9.3 against 15.5 us there with 16 tokens. ONEBIT_DECODE_VARIANT=1 / 2 in the environment forces the
+// warp-level mma.sp form / the tensor-memory form.
+bool use_legacy_decode(int64_t m, int64_t n, int64_t k) {
+  static const int forced = [] { const char* v = getenv("ONEBIT_DECODE_VARIANT"); return v ? atoi(v) : 0; }();
+  if (forced == 1) return true;
+  if (forced == 2) return false;
+  return n <= 8 && m * k <= 4096ll * 4096ll;
 }
 
 int check_dialect_rows(int dialect, int64_t m) {
@@ -132,7 +138,7 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
     e = ob::launch_gemm_prefill(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, status, stream);
     if (e != cudaSuccess) return cuda_fail(e, "tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = use_legacy_decode() ? ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, fresh_weights, stream)
+    e = use_legacy_decode(m, n, k) ? ob::launch_gemm_decode(bits_tile, meta_tile, scale, b, d, m, n, k, out_type, fresh_weights, stream)
                             : ob::launch_gemm_fewtok(bits_tile, meta_tile, scale, nullptr, b, d, m, n, k, out_type, false, fresh_weights, stream);
     if (e != cudaSuccess) return cuda_fail(e, "decode GEMM launch");
   } else {
@@ -203,7 +209,7 @@ int onebit_linear_tokens(const void* bits_tile, const void* meta_tile, const voi
     e = ob::launch_gemm_prefill_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, status, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major tensor-memory GEMM launch");
   } else if (kernel == ONEBIT_KERNEL_DECODE) {
-    e = use_legacy_decode() ? ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, fresh_weights, st)
+    e = use_legacy_decode(m, n, k) ? ob::launch_gemm_decode_tokens(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, fresh_weights, st)
                             : ob::launch_gemm_fewtok(bits_tile, meta_tile, scale, bias, x, y, m, n, k, out_type, true, fresh_weights, st);
     if (e != cudaSuccess) return cuda_fail(e, "token-major decode GEMM launch");
   } else {

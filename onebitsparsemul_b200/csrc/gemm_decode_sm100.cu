@@ -75,11 +75,8 @@ constexpr int kTmemE = 64, kTmemA = 96;
 constexpr int kPairs = kASlots / 2;      // slots are handed over in pairs of consecutive tiles: one commit per pair
 static_assert(kASlots == 4 && KL % 2 == 0, "the slot ring is indexed with masks; a round is whole pairs");
 static_assert(kTmemA + 32 * kASlots <= kTmemCols && kTmemE + 4 * kASlots <= kTmemA && 16 * kAccs <= kTmemE, "tensor memory plan");
-#ifdef OB_DBG_ONECTA
-constexpr int kMinSmem = 120 * 1024;
-#else
+constexpr int kProdWarp = 8, kMmaWarp = 9;   // weight stream; tensor-memory allocation and MMA issue
 constexpr int kMinSmem = 78 * 1024;      // at most two CTAs per SM, whatever the configuration needs
-#endif
 
 // NG = groups of 8 token columns per pass (the MMA is always N = 16; with NG = 1 both halves read the same tokens)
 template <int NG> struct FewTokCfg {
@@ -95,9 +92,7 @@ template <int NG> struct FewTokCfg {
   static constexpr int kNeeded = kWeights + kTokens + kRecv + kBars + 1024;   // + alignment slack
   static constexpr int kTotal = kNeeded < kMinSmem ? kMinSmem : kNeeded;
   static constexpr int kPieces = KL * 128 * NP / 8 / kWorkers;                // 16-byte token pieces per worker and round
-#ifndef OB_DBG_ONECTA
   static_assert(2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM must fit");
-#endif
   static_assert(KL * 128 * NP / 8 == kPieces * kWorkers, "a round's tokens are whole 16-byte pieces per worker");
 };
 
@@ -194,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     bulk_load(dst, a.meta_tile + tile * OB_TILE_META_BYTES, nt * OB_TILE_META_BYTES, bar_wfull(s));
     bulk_load(dst + KL * OB_TILE_META_BYTES, a.bits_tile + tile * OB_TILE_BITS_BYTES, nt * OB_TILE_BITS_BYTES, bar_wfull(s));
   };
-  if (warp == 8) {
+  if (warp == kProdWarp) {
     // ---------------- weight stream: round r of the slice -> ring slot r % kRing ----------------
     if (lane == 0) {
       // the barriers of the weight ring first, so that the first ring of loads is out as early as possible
@@ -210,7 +205,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       if (S > 1) mbar_expect_tx(bar_recv, (uint32_t)(S * rows_owned * npieces * 16));
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     tcgen05_alloc(tmem_slot, kTmemCols);
     // only now may CTAs of the next grid become resident beside this one
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -282,11 +277,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   const uint32_t tmem_base = *tmem_slot_gen;
   OB_TRACE_EV(2);
 
-#ifdef OB_DBG_LANE0POLL
-#define WORKER_WAIT(bar, par, code) do { if (lane == 0) mbar_wait(bar, par, budget, &g_fewtok_status, code); __syncwarp(); } while (0)
-#else
 #define WORKER_WAIT(bar, par, code) mbar_wait(bar, par, budget, &g_fewtok_status, code)
-#endif
   if (warp < 8) {
     // ---------------- workers: stage tokens, expand sign bits into tensor memory ----------------
     const int q = warp & 3, grp = warp >> 2;
@@ -312,9 +303,13 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
         // pair P of the slice = tiles 2P (first group of warps) and 2P + 1 (second group); its two operand slots
         // are handed back by one commit and handed over by one barrier
         const int P = r * (KL / 2) + pp, y = P & 1, j = 2 * pp + grp;
+        // Every warp waits for the pair's slots, also one whose group has no tile in the last pair of an odd slice:
+        // arriving below without this wait could complete the PREVIOUS use of the barrier while a slower warp has
+        // not yet written its quadrant, and the MMAs would read a stale operand.
+        WORKER_WAIT(bar_aempty(y), ((P >> 1) & 1) ^ 1, 203);
+        __syncwarp();        // the tcgen05 instructions below are .sync.aligned: no lane may still be in the wait loop
         if (j < nt) {
           const int t = r * KL + j, x = t & (kASlots - 1);
-          WORKER_WAIT(bar_aempty(y), ((P >> 1) & 1) ^ 1, 203);
           OB_TRACE_TILE(2, t);
           const uint2 w = *reinterpret_cast<const uint2*>(wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + j * OB_TILE_BITS_BYTES + row * 8);
           uint32_t v[32];
@@ -326,11 +321,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
           OB_TRACE_TILE(3, t);
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_afull(y));             // also for a missing second tile: the count is 8 warps
+        if (lane == 0) mbar_arrive(bar_afull(y));             // also without a tile: the count is 8 warps
       }
     }
     OB_TRACE_EV(4);
-  } else if (warp == 8) {
+  } else if (warp == kProdWarp) {
     // ---------------- weight stream: refill a slot once its round has been multiplied ----------------
     if (lane == 0) {
       for (int r = kRing; r < nrounds; ++r) {
@@ -351,19 +346,20 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
     const uint64_t tok_desc = make_desc(0, 128, (NG == 2) ? 2048u : 0u, kLayoutNone);
     const uint64_t meta_desc = make_desc(0, 128, 128, kLayoutNone);
-    int s = 0, rph = 0;                                       // ring slot and phase of the round
+    // One elect.sync for the whole loop: the elected lane runs it alone (a reconvergence of the warp after every
+    // pair of tiles cost ~400 cycles), and under the elect predicate the operands of the tcgen05 instructions stay
+    // warp-uniform values.
+    if (elect_one()) {
+      int s = 0, rph = 0;                                     // ring slot and phase of the round
 #pragma unroll 1
-    for (int r = 0; r < nrounds; ++r) {
-      const int nt = min(KL, T - r * KL);
+      for (int r = 0; r < nrounds; ++r) {
+        const int nt = min(KL, T - r * KL);
+        mbar_wait(bar_tfull(s), rph, budget, &g_fewtok_status, 205);
+        mbar_wait(bar_wfull(s), rph, budget, &g_fewtok_status, 206);
 #pragma unroll 1
-      for (int pp = 0; 2 * pp < nt; ++pp) {
-        const int P = r * (KL / 2) + pp, y = P & 1;
-        OB_TRACE_TILE(11, 2 * P);
-        if (elect_one()) {
-          if (pp == 0) {
-            mbar_wait(bar_tfull(s), rph, budget, &g_fewtok_status, 205);
-            mbar_wait(bar_wfull(s), rph, budget, &g_fewtok_status, 206);
-          }
+        for (int pp = 0; 2 * pp < nt; ++pp) {
+          const int P = r * (KL / 2) + pp, y = P & 1;
+          OB_TRACE_TILE(11, 2 * P);
           mbar_wait(bar_afull(y), (P >> 1) & 1, budget, &g_fewtok_status, 207);
           OB_TRACE_TILE(4, 2 * P);
           tcgen05_fence_after();
@@ -385,13 +381,13 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
             }
           }
           tcgen05_commit(bar_aempty(y));
-          if (2 * pp + 2 >= nt) tcgen05_commit(bar_wempty(s));   // the round's weights and tokens are free again
           OB_TRACE_TILE(5, 2 * P);
         }
+        tcgen05_commit(bar_wempty(s));                         // the round's weights and tokens are free again
+        if (++s == kRing) { s = 0; rph ^= 1; }
       }
-      if (++s == kRing) { s = 0; rph ^= 1; }
+      tcgen05_commit(bar_acc);
     }
-    if (elect_one()) tcgen05_commit(bar_acc);
   }
   __syncwarp();
 
@@ -410,6 +406,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     if (grp < NG) {
       const int row = q * 32 + lane;
       mbar_wait(bar_acc, 0, budget, &g_fewtok_status, 208);
+      __syncwarp();          // .sync.aligned loads follow
       tcgen05_fence_after();
       // the four accumulators, added in a fixed order
       float v[8];
@@ -478,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   OB_TRACE_EV(7);
   tcgen05_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tcgen05_fence_after();
     tcgen05_dealloc(tmem_base, kTmemCols);
   }

@@ -438,7 +438,7 @@ bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, 0)
 bt, mt = helpers.tile_order_from_canonical(canon, signs)
 t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
 d_bt, d_mt = t(bt), t(mt)
-for n in (1, 4, 5, 8, 12, 16):
+for n in (1, 4, 5, 7, 8, 12, 16):
     B = helpers.make_tokens(rng, k, n, "int")
     want, _ = oracle.gemm(bits, meta, 0, B, m)
     d_b = t(B)
@@ -455,13 +455,15 @@ print("decode ring ok")
 """
 
 
-@pytest.mark.parametrize("split", ["1", "2", "3", "5", "7", "8"])
-def test_decode_kernel_long_slices_exact(split):
+@pytest.mark.parametrize("variant,split", [("1", "1"), ("1", "2"), ("2", "1"), ("2", "2"), ("2", "3"), ("2", "5"), ("2", "7"), ("2", "8")])
+def test_decode_kernel_long_slices_exact(variant, split):
+    # both few-token kernels (1 = warp-level mma.sp, 2 = tensor memory), forced, with forced K splits: slices longer
+    # than the weight ring, an odd number of tiles, unequal slices, every token-staging path, both layouts
     import os
     import subprocess
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, ONEBIT_DECODE_SPLIT=split)
+    env = dict(os.environ, ONEBIT_DECODE_SPLIT=split, ONEBIT_DECODE_VARIANT=variant)
     r = subprocess.run([sys.executable, "-c", _DECODE_RING_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "decode ring ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
