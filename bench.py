@@ -274,6 +274,27 @@ def decode_extras(ob, _lib, dev):
                     "44 MB and 123 MB weights show the kernel's streaming rate"}
 
 
+def decode_loop_extras(ob, dev):
+    """The decode regime as a model sees it: a Llama-7B-shaped stack (4 blocks = 28 linear layers, 152 MB of packed
+    weights, more than L2) with every nn.Linear swapped for the one-bit layer, one step captured in a CUDA graph
+    and replayed per token."""
+    import torch
+    from onebitsparsemul_b200.decode_loop import LlamaShapedStack, measure_decode
+    peaks = load_peaks()
+    torch.cuda.empty_cache()
+    stack = LlamaShapedStack(blocks=4, hidden=4096, intermediate=11008, device=dev, seed=1)
+    replaced = ob.replace_linear_layers(stack)
+    out = {"model": "4 Llama-7B-shaped decoder blocks (q/k/v/o 4096x4096, gate/up 11008x4096, down 4096x11008), random weights, "
+                    "element-wise glue between the layers", "replaced_layers": replaced, "cases": []}
+    for tokens in (1, 8, 16):
+        r = measure_decode(stack, 4096, tokens=tokens, steps=30, device=dev)
+        r["frac_of_measured_hbm"] = round(r["weight_gbs"] / peaks["hbm_gbs"], 4)
+        out["cases"].append({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})
+    del stack
+    torch.cuda.empty_cache()
+    return out
+
+
 def bit_identity(ob, _lib, oracle, layer, S, world, rank, dev, reduce_minmax):
     """Outside the timed region, integer tokens (every partial sum exact): the sharded job against the oracle
     and the ranks against each other. Returns a dict of booleans on every rank (rank 0's oracle verdict is
@@ -474,9 +495,10 @@ def run_ours(args):
                   "traffic": MEASURED_TRAFFIC.get(q), "note": "8.4 ms of work: burst clocks"}
         del pw8, B8, C8
 
-    decode = None
+    decode = decode_loop = None
     if rank == 0 and world == 1 and not args.no_decode:
         decode = decode_extras(ob, _lib, dev)
+        decode_loop = decode_loop_extras(ob, dev)
     sync_all()
 
     if rank == 0:
@@ -525,6 +547,8 @@ def run_ours(args):
             line["square8192"] = square
         if decode is not None:
             line["decode"] = decode
+        if decode_loop is not None:
+            line["decode_loop"] = decode_loop
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -152,6 +152,14 @@ int onebit_pack_from_dense(const void *dense, int dense_dtype, int64_t m, int64_
                            void *a_bits, void *e_meta, int meta_dialect, void *bits_tile, void *meta_tile,
                            void *stream);
 
+/* The whole of BinaryLinear_2_4.pack (onebit_sparse_mul/__init__.py:130-145) in ONE pass over unmasked fp16
+ * weights: mask_creator (_semi_structured_conversions.py:286-314; tie rule as onebit_mask24) applied in registers,
+ * then everything onebit_pack_from_dense does. Bit-exact with onebit_mask24 followed by onebit_pack_from_dense,
+ * without writing and re-reading the masked copy; masked_f16 (m, k) receives that copy only if it is not NULL.
+ * Same shape rules and nullable outputs as onebit_pack_from_dense. */
+int onebit_mask_pack_from_dense(const void *dense_f16, int64_t m, int64_t k, void *masked_f16, void *sparse, void *a_bits,
+                                void *e_meta, int meta_dialect, void *bits_tile, void *meta_tile, void *stream);
+
 /* Magnitude 2:4 mask of fp16 weights (mask_creator, _semi_structured_conversions.py:286-314): in
  * every group of 4 the two smallest |w| are dropped; among equal magnitudes the lower index is
  * dropped first. masked (fp16, same shape) and mask (uint8 0/1) may each be NULL. count % 8 == 0. */

@@ -151,6 +151,27 @@ class PackedWeight:
         self.packed_binary_sparse, self.meta = packed_binary_sparse, meta
         self.stable = stable
 
+    # -- persistence (packed_file.py) ---------------------------------------------------------------------
+    def save(self, path, bias=None, row0=0, rows_total=None, slab=0, slabs=1):
+        """Write the tile-ordered operands (and scale, optional bias) to `path`; see packed_file.py for the
+        format. `row0` / `rows_total` / `slab` / `slabs` place a row slab inside a sharded matrix."""
+        from . import packed_file
+        if self.bits_tile is None:
+            raise ValueError("only tile-ordered weights (m, k multiples of 128) can be saved")
+        packed_file.save_packed(path, self.bits_tile, self.meta_tile, self.m, self.k, order=packed_file.ORDER_TILE,
+                                scale=self.scale, bias=bias, row0=row0, rows_total=rows_total, slab=slab, slabs=slabs)
+
+    @classmethod
+    def load(cls, path, device="cuda"):
+        """Read a file written by `save` (tile order) or holding reference-ordered operands (those are brought into
+        tile order on the GPU). Returns (PackedWeight, bias or None, PackedFileInfo)."""
+        from . import packed_file
+        info, bits, meta, scale, bias = packed_file.load_packed(path, device)
+        if info.order == packed_file.ORDER_TILE:
+            return cls(info.m, info.k, bits, meta, scale), bias, info
+        pw = relayout(bits, meta, meta_dialect=info.order, scale=scale)
+        return pw, bias, info
+
     def _selector(self, kernel):
         """The kernel selector of the next GEMM on these weights, with the stable-weights flag."""
         flag = KERNEL_STABLE_WEIGHTS if self.stable else 0
@@ -166,20 +187,20 @@ def pack_weight(weight, scale=None, apply_mask=True, keep_reference=True, meta_d
     w = _cuda(weight).contiguous()
     m, k = w.shape
     dev = w.device
+    if apply_mask and w.dtype != torch.float16:
+        raise TypeError("the GPU mask takes float16 weights; pass apply_mask=False for pre-masked input")
     with torch.cuda.device(dev):
-        if apply_mask:
-            if w.dtype != torch.float16:
-                raise TypeError("the GPU mask kernel takes float16 weights; pass apply_mask=False for pre-masked input")
-            masked = torch.empty_like(w)
-            _lib.check(lib.onebit_mask24(_ptr(w), w.numel(), _ptr(masked), None, _stream()))
-            w = masked
         tiled = m % 128 == 0 and k % 128 == 0
         bits_tile = torch.empty(m * k // 16, dtype=torch.uint8, device=dev) if tiled else None
         meta_tile = torch.empty(m * k // 8, dtype=torch.uint8, device=dev) if tiled else None
         a_bits = torch.empty((k // 2, m // 8), dtype=torch.uint8, device=dev) if keep_reference else None
         e_meta = torch.empty((m, k // 16), dtype=torch.int16, device=dev) if keep_reference else None
-        _lib.check(lib.onebit_pack_from_dense(_ptr(w), _dense_code(w.dtype), m, k, None, _ptr(a_bits), _ptr(e_meta),
-                                              meta_dialect, _ptr(bits_tile), _ptr(meta_tile), _stream()))
+        if apply_mask:                                       # mask, compress, encode, quantise, bit-pack: one pass
+            _lib.check(lib.onebit_mask_pack_from_dense(_ptr(w), m, k, None, None, _ptr(a_bits), _ptr(e_meta), meta_dialect,
+                                                       _ptr(bits_tile), _ptr(meta_tile), _stream()))
+        else:
+            _lib.check(lib.onebit_pack_from_dense(_ptr(w), _dense_code(w.dtype), m, k, None, _ptr(a_bits), _ptr(e_meta),
+                                                  meta_dialect, _ptr(bits_tile), _ptr(meta_tile), _stream()))
     if scale is not None:
         scale = _cuda(scale).to(torch.float16).contiguous()
     return PackedWeight(m, k, bits_tile, meta_tile, scale, a_bits, e_meta)
@@ -374,6 +395,29 @@ class BinaryLinear_2_4(nn.Module):
         self.packed_flag = torch.ones((), dtype=torch.uint8, device=dev)
         self.vaild = True
         self._weights_stable = False
+
+    def save_packed(self, path):
+        """Store this layer's packed operands, scale and bias in one file (packed_file.py); `from_packed_file` is
+        the inverse. The reference-ordered twins are not stored: they are an exchange format, not what runs."""
+        if not self.vaild:
+            raise NotImplementedError("the BinaryLinear")
+        self._packed().save(path, bias=self.bias)
+
+    @classmethod
+    def from_packed_file(cls, path, device="cuda", out_dtype=torch.float16) -> "BinaryLinear_2_4":
+        pw, bias, info = PackedWeight.load(path, device)
+        if info.slabs != 1:
+            raise ValueError(f"{path} holds slab {info.slab} of {info.slabs}: load it through ShardedBinaryLinear")
+        layer = cls(info.k, info.m, out_dtype=out_dtype, bias=bias is not None).to(device)
+        layer.bits_tile, layer.meta_tile = pw.bits_tile, pw.meta_tile
+        if pw.scale is not None:
+            layer.scale = pw.scale
+        if bias is not None:
+            layer.bias = bias
+        layer.packed_flag = torch.ones((), dtype=torch.uint8, device=layer.bits_tile.device)
+        layer.vaild = True
+        layer._weights_stable = False
+        return layer
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, out_dtype=torch.float16) -> "BinaryLinear_2_4":

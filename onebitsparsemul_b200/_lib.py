@@ -33,6 +33,7 @@ SIGNATURES = {
     "onebit_matmul_packed_scatter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "onebit_matmul_packed_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "onebit_pack_from_dense": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
+    "onebit_mask_pack_from_dense": (_int, [_vp, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp, _vp]),
     "onebit_mask24": (_int, [_vp, _i64, _vp, _vp, _vp]),
     "onebit_unpack_to_dense": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "onebit_check_device_status": (_int, []),

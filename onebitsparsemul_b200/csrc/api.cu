@@ -288,8 +288,9 @@ int onebit_sparse_matmul_ex(const void* a_bits, const void* b, void* d, const vo
   return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "cudaEventRecord(scratch)");
 }
 
-int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits,
-                           void* e_meta, int meta_dialect, void* bits_tile, void* meta_tile, void* stream) {
+namespace {
+int pack_impl(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits, void* e_meta, int meta_dialect,
+              void* bits_tile, void* meta_tile, bool apply_mask, void* masked, void* stream) {
   if (!dense) return fail(ONEBIT_ERR_NULL, "null dense pointer");
   if (dense_dtype < OB_DENSE_F16 || dense_dtype > OB_DENSE_I32) return fail(ONEBIT_ERR_ARG, "unknown dense dtype %d", dense_dtype);
   if (m <= 0 || k <= 0 || k % 32 != 0 || m % 32 != 0)
@@ -297,9 +298,20 @@ int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_
   if (e_meta) { if (int rc = check_dialect_rows(meta_dialect, m)) return rc; }
   if ((bits_tile || meta_tile) && !tiled_shape(m, k))
     return fail(ONEBIT_ERR_SHAPE, "tile order needs m %% 128 == 0 and k %% 128 == 0 (got m=%lld k=%lld)", (long long)m, (long long)k);
-  cudaError_t e = ob::launch_pack(dense, dense_dtype, m, k, sparse, a_bits, e_meta, meta_dialect, bits_tile, meta_tile,
-                                  static_cast<cudaStream_t>(stream));
+  cudaError_t e = ob::launch_pack(dense, dense_dtype, m, k, sparse, a_bits, e_meta, meta_dialect, bits_tile, meta_tile, apply_mask,
+                                  masked, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? ONEBIT_OK : cuda_fail(e, "pack launch");
+}
+}  // namespace
+
+int onebit_pack_from_dense(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse, void* a_bits,
+                           void* e_meta, int meta_dialect, void* bits_tile, void* meta_tile, void* stream) {
+  return pack_impl(dense, dense_dtype, m, k, sparse, a_bits, e_meta, meta_dialect, bits_tile, meta_tile, false, nullptr, stream);
+}
+
+int onebit_mask_pack_from_dense(const void* dense_f16, int64_t m, int64_t k, void* masked_f16, void* sparse, void* a_bits,
+                                void* e_meta, int meta_dialect, void* bits_tile, void* meta_tile, void* stream) {
+  return pack_impl(dense_f16, OB_DENSE_F16, m, k, sparse, a_bits, e_meta, meta_dialect, bits_tile, meta_tile, true, masked_f16, stream);
 }
 
 int onebit_mask24(const void* dense_f16, int64_t count, void* masked_f16, void* mask_u8, void* stream) {

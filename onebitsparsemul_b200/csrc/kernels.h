@@ -9,9 +9,10 @@ namespace ob {
 int sm_count();
 
 // K1 (pack.cu)
+// apply_mask (fp16 only): the 2:4 magnitude mask is applied in the same pass; masked (nullable) receives the masked weights
 cudaError_t launch_pack(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse,
                         void* bits_ref, void* meta_ref, int dialect, void* bits_tile, void* meta_tile,
-                        cudaStream_t stream);
+                        bool apply_mask, void* masked, cudaStream_t stream);
 // 2:4 magnitude mask (mask.cu)
 cudaError_t launch_mask24(const void* dense_f16, int64_t count, void* masked_f16, void* mask_u8,
                           cudaStream_t stream);

@@ -7,24 +7,9 @@
 #include <stdint.h>
 
 #include "kernels.h"
+#include "mask24.h"
 
 namespace {
-
-__device__ __forceinline__ unsigned keep_mask4(const uint16_t* w) {
-  unsigned keep = 0;
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const unsigned at = w[t] & 0x7fffu;       // |w| of an fp16 orders like its low 15 bits; NaN last
-    int rank = 0;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const unsigned au = w[u] & 0x7fffu;
-      rank += (au < at) || (au == at && u < t);
-    }
-    keep |= (rank >= 2 ? 1u : 0u) << t;
-  }
-  return keep;
-}
 
 __global__ void __launch_bounds__(256) ob_mask24_kernel(const uint4* __restrict__ dense, int64_t vecs,
                                                         uint4* __restrict__ masked, uint2* __restrict__ mask) {
@@ -32,7 +17,7 @@ __global__ void __launch_bounds__(256) ob_mask24_kernel(const uint4* __restrict_
   if (i >= vecs) return;
   uint4 v = __ldg(dense + i);
   uint16_t* w = reinterpret_cast<uint16_t*>(&v);
-  const unsigned keep = keep_mask4(w) | (keep_mask4(w + 4) << 4);
+  const unsigned keep = ob_keep_mask4(w) | (ob_keep_mask4(w + 4) << 4);
   if (mask) {
     uint2 mk;
     uint8_t* mb = reinterpret_cast<uint8_t*>(&mk);
@@ -44,7 +29,7 @@ __global__ void __launch_bounds__(256) ob_mask24_kernel(const uint4* __restrict_
     // the reference multiplies by the 0/1 mask: a dropped weight becomes a signed zero, a kept NaN stays
 #pragma unroll
     for (int t = 0; t < 8; ++t)
-      if (!((keep >> t) & 1u)) w[t] = ((w[t] & 0x7fffu) > 0x7c00u) ? w[t] : (uint16_t)(w[t] & 0x8000u);
+      if (!((keep >> t) & 1u)) w[t] = ob_dropped_value(w[t]);
     masked[i] = v;
   }
 }

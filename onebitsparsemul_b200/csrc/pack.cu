@@ -10,12 +10,18 @@
 // the 4 nibbles of a chunk are one lane's private work. Everything is staged in shared memory and
 // leaves the SM as 16-byte stores. HBM-bound: 2 bytes read and at most ~0.6 byte written per dense
 // weight.
+//
+// Fused form (fp16 only): the 2:4 magnitude mask of mask_creator (_semi_structured_conversions.py:286-314)
+// is applied to the 16 values a lane has just loaded, before they are encoded, so that the whole of
+// BinaryLinear_2_4.pack -- mask, compress, encode, quantise, bit-pack -- is ONE pass over the dense weights:
+// the masked copy is never written and read back (it is written only if the caller asks for it).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "formats.h"
 #include "kernels.h"
+#include "mask24.h"
 
 namespace {
 
@@ -45,6 +51,8 @@ struct PackArgs {
   int dialect;
   uint32_t* bits_tile; // tile-ordered sign bits                       (nullable; needs m,k % 128 == 0)
   uint16_t* meta_tile; // tile-ordered metadata                        (nullable; needs m,k % 128 == 0)
+  int apply_mask;      // fp16 only: mask every group of 4 to its two largest magnitudes first
+  void* masked;        // (m, k) the masked weights, fp16                (nullable; with apply_mask)
 };
 
 template <int DT>
@@ -84,6 +92,23 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
     } else {
 #pragma unroll
       for (int t = 0; t < 16; ++t) e[t] = T(0);
+    }
+
+    if constexpr (DT == OB_DENSE_F16) {
+      if (a.apply_mask && valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const unsigned keep = ob_keep_mask4(&e[4 * g]);
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            if (!((keep >> t) & 1u)) e[4 * g + t] = ob_dropped_value(e[4 * g + t]);
+        }
+        if (a.masked) {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.masked) + row * a.k + chunk * 16);
+          dst[0] = *reinterpret_cast<uint4*>(&e[0]);
+          dst[1] = *reinterpret_cast<uint4*>(&e[8]);
+        }
+      }
     }
 
     unsigned meta = 0, signs = 0;
@@ -179,9 +204,10 @@ namespace ob {
 
 cudaError_t launch_pack(const void* dense, int dense_dtype, int64_t m, int64_t k, void* sparse,
                         void* bits_ref, void* meta_ref, int dialect, void* bits_tile, void* meta_tile,
-                        cudaStream_t stream) {
+                        bool apply_mask, void* masked, cudaStream_t stream) {
+  if (apply_mask && dense_dtype != OB_DENSE_F16) return cudaErrorInvalidValue;
   PackArgs a{dense, m, k, sparse, static_cast<uint8_t*>(bits_ref), static_cast<uint16_t*>(meta_ref),
-             dialect, static_cast<uint32_t*>(bits_tile), static_cast<uint16_t*>(meta_tile)};
+             dialect, static_cast<uint32_t*>(bits_tile), static_cast<uint16_t*>(meta_tile), apply_mask ? 1 : 0, masked};
   dim3 grid((unsigned)((k + 127) / 128), (unsigned)((m + 127) / 128));
   switch (dense_dtype) {
     case OB_DENSE_F16: ob_pack_kernel<OB_DENSE_F16><<<grid, 256, 0, stream>>>(a); break;

@@ -90,6 +90,23 @@ class ShardedBinaryLinear:
         sl = slice(self.start, self.start + self.rows)
         return self.pack_slab(weight[sl], None if scale is None else scale[sl], apply_mask)
 
+    # -- persistence: one file per row slab, every rank touches only its own ------------------------------------
+    def save(self, directory: str, name: str):
+        """Write this rank's slab to `directory` (packed_file.slab_path names the file)."""
+        from . import packed_file
+        self.packed.save(packed_file.slab_path(directory, name, self.rank, self.world), row0=self.start, rows_total=self.m,
+                         slab=self.rank, slabs=self.world)
+
+    def load(self, directory: str, name: str, device="cuda"):
+        """Read this rank's slab; the file must have been written for the same partition."""
+        from . import PackedWeight, packed_file
+        path = packed_file.slab_path(directory, name, self.rank, self.world)
+        pw, _, info = PackedWeight.load(path, device)
+        if (info.row0, info.m, info.k, info.rows_total, info.slabs) != (self.start, self.rows, self.k, self.m, self.world):
+            raise packed_file.PackedFileError(f"{path} was written for another partition of the matrix")
+        self.packed = pw
+        return self
+
     # -- GEMM ---------------------------------------------------------------------------------------------
     def _gemm(self, B, out, row0=0, rows=None):
         rows = self.rows if rows is None else rows

@@ -10,6 +10,7 @@ import pytest
 import torch
 
 import oracle
+from onebitsparsemul_b200 import _lib
 from tests import helpers
 
 pytestmark = pytest.mark.gpu
@@ -156,3 +157,39 @@ def test_host_buffer_entry_point_equals_device_path(m, n, k):
             assert torch.equal(Ch, want.cpu())
     with pytest.raises(ValueError):
         ob.matmul_packed_host(pw, torch.zeros((k, n), dtype=torch.float16))     # not pinned
+
+
+def test_llama_shaped_stack_replace_and_graph_decode_loop():
+    """The reference's model-replace flow (tests/python/test_model_replace.py:22-44) on a Llama-shaped stack, and the
+    decode loop a model runs: one token at a time through a CUDA graph. The graph must give the bits of the eager
+    run, and the replaced stack must equal the same stack evaluated with the dequantised weights."""
+    import onebitsparsemul_b200 as ob
+    from onebitsparsemul_b200.decode_loop import GraphedDecoder, LlamaShapedStack, measure_decode
+    hidden, inter = 512, 1408
+    stack = LlamaShapedStack(blocks=2, hidden=hidden, intermediate=inter, device="cuda", seed=5)
+    ref = LlamaShapedStack(blocks=2, hidden=hidden, intermediate=inter, device="cuda", seed=5)
+    assert ob.replace_linear_layers(stack) == 14
+    # reference stack: the same layers with the dequantised one-bit weights as dense fp32 matrices
+    for blk, rblk in zip(stack.blocks, ref.blocks):
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"):
+            packed = getattr(blk, name)
+            dense = torch.empty((packed.outfeatures, packed.infeatures), dtype=torch.float16, device="cuda")
+            _lib.check(_lib.load().onebit_unpack_to_dense(packed.bits_tile.data_ptr(), packed.meta_tile.data_ptr(), packed.scale.data_ptr(),
+                                                          packed.outfeatures, packed.infeatures, dense.data_ptr(), None))
+            getattr(rblk, name).weight.data = dense
+    torch.manual_seed(3)
+    ref = ref.float()
+    for tokens in (1, 4, 40):
+        x = torch.randn((tokens, hidden), device="cuda").to(torch.float16)
+        with torch.no_grad():
+            eager = stack(x)
+            want = ref(x.float())
+        assert torch.isfinite(eager).all()
+        err = (eager.float() - want.float()).abs().max().item()
+        assert err <= 2e-2 * want.float().abs().max().item() + 1e-3, err
+        dec = GraphedDecoder(stack, tokens, hidden)
+        for _ in range(3):                                      # replays are repeatable and equal the eager run
+            assert torch.equal(dec.step(x), eager)
+        _lib.check(_lib.load().onebit_check_device_status())
+    m = measure_decode(stack, hidden, tokens=1, steps=5)
+    assert m["linear_layers"] == 14 and m["us_per_step"] > 0

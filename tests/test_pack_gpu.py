@@ -113,6 +113,63 @@ def test_mask_matches_reference_and_oracle(lib, golden):
     assert (mask.cpu().numpy().reshape(-1, 4).sum(1) == 2).all()
 
 
+@pytest.mark.parametrize("m,k", [(128, 128), (256, 384), (1024, 4096), (64, 32)])
+def test_fused_mask_and_pack_equals_the_two_passes(lib, golden, m, k):
+    # unmasked weights with ties, signed zeros, infinities and NaNs: the one-pass kernel must give, byte for byte,
+    # what the mask kernel followed by the pack kernel gives -- and the reference's own mask on tie-free data
+    rng = np.random.default_rng(m + k)
+    dense = (rng.standard_normal((m, k)) * 2).astype(np.float16)
+    dense[rng.random((m, k)) < 0.15] = np.float16(0.0)
+    dense[rng.random((m, k)) < 0.05] = np.float16(-0.0)
+    dense[rng.random((m, k)) < 0.1] = np.float16(1.0)                      # ties
+    dense[rng.random((m, k)) < 0.01] = np.float16(np.nan)
+    dense[rng.random((m, k)) < 0.01] = np.float16(np.inf)
+    d = dev(dense)
+    tiled = m % 128 == 0 and k % 128 == 0
+
+    def outputs():
+        o = dict(masked=torch.zeros_like(d), sparse=torch.zeros((m, k // 2), dtype=torch.float16, device="cuda"),
+                 bits=torch.zeros((k // 2, m // 8), dtype=torch.uint8, device="cuda"),
+                 meta=torch.zeros((m, k // 16), dtype=torch.int16, device="cuda"))
+        if tiled:
+            o.update(bits_tile=torch.zeros(m * k // 16, dtype=torch.uint8, device="cuda"),
+                     meta_tile=torch.zeros(m * k // 8, dtype=torch.uint8, device="cuda"))
+        return o
+
+    ptr = lambda o, name: o[name].data_ptr() if name in o else None
+    two, one = outputs(), outputs()
+    _lib.check(lib.onebit_mask24(d.data_ptr(), d.numel(), two["masked"].data_ptr(), None, None))
+    _lib.check(lib.onebit_pack_from_dense(two["masked"].data_ptr(), _lib.DENSE_F16, m, k, two["sparse"].data_ptr(), two["bits"].data_ptr(),
+                                          two["meta"].data_ptr(), _lib.META_PYTHON, ptr(two, "bits_tile"), ptr(two, "meta_tile"), None))
+    _lib.check(lib.onebit_mask_pack_from_dense(d.data_ptr(), m, k, one["masked"].data_ptr(), one["sparse"].data_ptr(), one["bits"].data_ptr(),
+                                               one["meta"].data_ptr(), _lib.META_PYTHON, ptr(one, "bits_tile"), ptr(one, "meta_tile"), None))
+    for name in two:
+        a, b = two[name].cpu().numpy(), one[name].cpu().numpy()
+        assert (a.view(np.uint8) == b.view(np.uint8)).all(), name
+    # without the optional masked copy the packed outputs are the same
+    again = outputs()
+    _lib.check(lib.onebit_mask_pack_from_dense(d.data_ptr(), m, k, None, None, again["bits"].data_ptr(), again["meta"].data_ptr(),
+                                               _lib.META_PYTHON, ptr(again, "bits_tile"), ptr(again, "meta_tile"), None))
+    assert torch.equal(again["bits"], one["bits"]) and torch.equal(again["meta"], one["meta"])
+    # non-fp16 weights are refused
+    assert lib.onebit_mask_pack_from_dense(None, m, k, None, None, None, None, 0, None, None, None) == 2
+
+
+def test_fused_mask_and_pack_on_the_reference_golden(lib, golden):
+    # the reference's mask_creator on tie-free data, then its pack: here in one pass from the unmasked weights
+    dense = golden["mask_dense"]
+    m, k = dense.shape
+    if m % 64 or k % 32:
+        pytest.skip("golden mask case is not pack-shaped")
+    d = dev(dense)
+    bits = torch.zeros((k // 2, m // 8), dtype=torch.uint8, device="cuda")
+    meta = torch.zeros((m, k // 16), dtype=torch.int16, device="cuda")
+    _lib.check(lib.onebit_mask_pack_from_dense(d.data_ptr(), m, k, None, None, bits.data_ptr(), meta.data_ptr(), _lib.META_PYTHON, None, None, None))
+    masked = dense * golden["mask_mask"].astype(np.float16)
+    want_bits, want_meta = oracle.pack(masked, oracle.META_PYTHON)
+    assert (bits.cpu().numpy() == want_bits).all() and (meta.cpu().numpy() == want_meta).all()
+
+
 def test_python_api_pack_round_trip(golden):
     import onebitsparsemul_b200 as ob
     dense = torch.from_numpy(golden["f16_dense"])
