@@ -295,6 +295,49 @@ def decode_loop_extras(ob, dev):
     return out
 
 
+def context_baselines(dev, sizes):
+    """Numbers that put the headline in context, outside the timed region: the reference's own host check GEMM
+    (the CUTLASS template its CLI instantiates, one core, 512^3 -- the size of the reference's CPU-runnable
+    configuration) and cuBLAS dense fp16 through torch.matmul at the benchmark sizes."""
+    import torch
+    out = {}
+    try:
+        from oracle import build_ref
+        r = build_ref.run(512, 512, 512)
+        if r is not None:
+            out["reference_host_gemm_512"] = {"seconds": r[0], "gflops": r[1], "cores": 1, "kind": "reference",
+                                              "what": "cutlass::reference::host::Gemm<half, ColumnMajor, half, RowMajor, float, RowMajor, "
+                                                      "float, float>, the instantiation of the reference's --reference-check, dense-equivalent "
+                                                      "GFLOP/s of 512^3"}
+        else:
+            out["reference_host_gemm_512"] = "unavailable on this box: oracle/_ref was not built (no CUTLASS copy)"
+    except Exception as exc:
+        out["reference_host_gemm_512"] = f"failed: {exc}"[:200]
+    dense = {}
+    for q in sizes:
+        try:
+            W = torch.randn((q, q), device=dev, dtype=torch.float32).to(torch.float16)
+            B = torch.randn((q, q), device=dev, dtype=torch.float32).to(torch.float16)
+            C = torch.empty((q, q), device=dev, dtype=torch.float16)
+            for _ in range(3):
+                torch.matmul(W, B, out=C)
+            torch.cuda.synchronize()
+            steps = 20 if q <= 8192 else 6
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                torch.matmul(W, B, out=C)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            dense[str(q)] = {"ms": ms, "tflops": 2.0 * q ** 3 / (ms * 1e-3) / 1e12}
+            del W, B, C
+        except Exception as exc:
+            dense[str(q)] = f"failed: {exc}"[:200]
+    out["torch_matmul_dense_fp16"] = dense
+    return out
+
+
 def bit_identity(ob, _lib, oracle, layer, S, world, rank, dev, reduce_minmax):
     """Outside the timed region, integer tokens (every partial sum exact): the sharded job against the oracle
     and the ranks against each other. Returns a dict of booleans on every rank (rank 0's oracle verdict is
@@ -495,10 +538,11 @@ def run_ours(args):
                   "traffic": MEASURED_TRAFFIC.get(q), "note": "8.4 ms of work: burst clocks"}
         del pw8, B8, C8
 
-    decode = decode_loop = None
+    decode = decode_loop = context = None
     if rank == 0 and world == 1 and not args.no_decode:
         decode = decode_extras(ob, _lib, dev)
         decode_loop = decode_loop_extras(ob, dev)
+        context = context_baselines(dev, sorted({8192, S}))
     sync_all()
 
     if rank == 0:
@@ -549,6 +593,8 @@ def run_ours(args):
             line["decode"] = decode
         if decode_loop is not None:
             line["decode_loop"] = decode_loop
+        if context is not None:
+            line["context"] = context
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

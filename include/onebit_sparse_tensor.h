@@ -85,7 +85,8 @@ int onebit_sparse_matmul_ex(const void *a_bits, const void *b, void *d, const vo
 
 /* Reference order -> tile order; the once-per-weight half of onebit_sparse_matmul_ex. It is the
  * device-side counterpart of handing pack()'s tensors (onebit_sparse_mul/__init__.py:130-145) to
- * the kernel. */
+ * the kernel. All four buffers must be 16-byte aligned (so must a_bits and e_meta of the stateless entry
+ * points; the reference's kernel asks the same of its A and E operands, csrc/kernel.h:19-21). */
 int onebit_relayout(const void *a_bits, const void *e_meta, int meta_dialect, int64_t m, int64_t k,
                     void *bits_tile, void *meta_tile, void *stream);
 

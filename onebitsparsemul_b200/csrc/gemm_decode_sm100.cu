@@ -516,7 +516,7 @@ cudaError_t launch(const FewTokArgs& a, int S, cudaStream_t stream) {
 // 2 x SMs CTAs; a CTA costs a fixed start-up (allocation, barriers, one DRAM round trip) plus its tiles, and a
 // split costs the hand-off of the partial sums. S minimises waves x (start-up + tiles) + hand-off in that model,
 // whose constants are cycles measured with the kernel's own timeline.
-int pick_split(int64_t m, int64_t k) {
+int pick_split(int64_t m, int64_t k, int64_t token_blocks) {
   const int64_t tiles_k = k / OB_TILE_K, row_blocks = m / 128;
   const long long wave = 2ll * ob::sm_count();
   constexpr long long kStart = 2500, kTile = 270, kHandOff = 800;
@@ -524,7 +524,8 @@ int pick_split(int64_t m, int64_t k) {
   long long best_cost = LLONG_MAX;
   for (int S = 1; S <= 8; ++S) {
     if (tiles_k < S) break;
-    const long long ctas = row_blocks * S, waves = (ctas + wave - 1) / wave, T = (tiles_k + S - 1) / S;
+    // every block of 16 token columns is a grid of its own along z and streams the weights again (from L2)
+    const long long ctas = row_blocks * S * token_blocks, waves = (ctas + wave - 1) / wave, T = (tiles_k + S - 1) / S;
     const long long cost = waves * (kStart + T * kTile) + (S > 1 ? kHandOff : 0);
     if (cost < best_cost) { best = S; best_cost = cost; }
   }
@@ -536,7 +537,7 @@ int pick_split(int64_t m, int64_t k) {
 template <bool TM>
 cudaError_t dispatch(const FewTokArgs& a, int out_type, cudaStream_t stream) {
   const bool two = (a.n > 8);
-  const int S = pick_split(a.m, a.k);
+  const int S = pick_split(a.m, a.k, two ? (a.n + 15) / 16 : 1);
   if (out_type == OB_OUT_F16) return two ? launch<2, __half, TM>(a, S, stream) : launch<1, __half, TM>(a, S, stream);
   return two ? launch<2, float, TM>(a, S, stream) : launch<1, float, TM>(a, S, stream);
 }

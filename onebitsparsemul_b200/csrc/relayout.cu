@@ -5,7 +5,7 @@
 // onebit_sparse_mul/_semi_structured_conversions.py:21-48). The GEMM kernels of this library read
 // 128x128 tiles whose sign bits are row-major in k and whose metadata is laid out for tensor
 // memory. This kernel is the bit transpose between the two; one CTA per tile, HBM-bound
-// (3/16 byte read and written per dense weight).
+// (3/16 byte read and written per dense weight). The operands must be 16-byte aligned.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -14,37 +14,59 @@
 
 namespace {
 
-__global__ void __launch_bounds__(256) ob_relayout_kernel(const uint32_t* __restrict__ bits_ref,
+// One CTA per 128 x 128 tile. Everything enters and leaves the SM as 16-byte accesses: in the reference orders the
+// tile's sign bits are 64 segments of 16 bytes (128 rows of one bitfield column each) and its metadata is 4 runs of
+// 512 bytes (one per pair of 16-column chunks: the row shuffles of both dialects stay inside a 128-row block);
+// both are staged in shared memory, permuted there, and stored in tile order.
+__global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restrict__ bits_ref,
                                                           const uint16_t* __restrict__ meta_ref, int dialect,
                                                           int64_t m, int64_t k, uint32_t* __restrict__ bits_tile,
                                                           uint16_t* __restrict__ meta_tile) {
+  __shared__ __align__(16) uint32_t s_bits[64 * 4];        // [kept value of the tile row][32-row group]
+  __shared__ __align__(16) uint16_t s_meta[4 * 256];       // [chunk pair][shuffled row][2]
+  __shared__ __align__(16) uint32_t s_out[256];            // the tile's sign block in tile order
   const int64_t kb = blockIdx.x, mb = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int64_t tile = mb * (k / 128) + kb;
 
-  // sign bits: warp = (32-row group, half of the 64 kept values). Lane l fetches the bitfield word
-  // of the kept value whose tile-order bit position is l; ballot j then is tile row j's word.
+  if (t < 64) {
+    reinterpret_cast<uint4*>(s_bits)[t] = __ldg(reinterpret_cast<const uint4*>(bits_ref + ((kb * 64 + t) * m + mb * 128) / 8));
+  } else if (t < 192) {
+    const int pair = (t - 64) >> 5, j = (t - 64) & 31;     // 512 bytes per pair = 32 x 16 bytes
+    reinterpret_cast<uint4*>(s_meta)[t - 64] = __ldg(reinterpret_cast<const uint4*>(meta_ref + (kb * 4 + pair) * 2 * m + mb * 256 + j * 8));
+  }
+  __syncthreads();
+
+  // sign bits: warp = (32-row group, half of the 64 kept values). Lane l takes the bitfield word of the kept
+  // value whose tile-order bit position is l; ballot j then is tile row j's word.
   {
     const int rg = warp & 3, half = warp >> 2;
     const int q_local = half * 32 + 2 * (lane & 15) + (lane >> 4);
-    const int64_t q = kb * 64 + q_local;
-    const uint32_t w = __ldg(&bits_ref[(q * m + mb * 128 + rg * 32) >> 5]);
+    const uint32_t w = s_bits[q_local * 4 + rg];
     uint32_t mine = 0;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const uint32_t b = __ballot_sync(0xffffffffu, (w >> j) & 1u);
       if (lane == j) mine = b;
     }
-    bits_tile[tile * 256 + (rg * 32 + lane) * 2 + half] = mine;
+    s_out[(rg * 32 + lane) * 2 + half] = mine;
   }
-  // metadata: gather through the reference order, store in tile order (consecutive threads write
-  // consecutive uint16 of the tile block)
-  for (int i = threadIdx.x; i < 1024; i += 256) {
-    const int u = i >> 3, wd = i & 7;
-    const int r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4, c2 = wd >> 1, r1 = wd & 1;
-    const int64_t row = mb * 128 + r0 + 8 * r1 + 16 * r2, chunk = kb * 8 + 2 * c2 + c1;
-    meta_tile[tile * 1024 + i] = __ldg(&meta_ref[ob_meta_ref_offset(dialect, m, row, chunk)]);
+  // metadata: thread u < 128 assembles lane u of the tile block (8 words: chunk pairs c2 = 0..3, rows r and r + 8)
+  if (t < 128) {
+    const int u = t, r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4;
+    __align__(16) uint16_t out[8];
+#pragma unroll
+    for (int wd = 0; wd < 8; ++wd) {
+      const int c2 = wd >> 1, r1 = wd & 1;
+      const int64_t row = mb * 128 + r0 + 8 * r1 + 16 * r2, chunk = kb * 8 + 2 * c2 + c1;
+      int64_t rs, cs;
+      ob_meta_ref_position(dialect, row, chunk, &rs, &cs);
+      out[wd] = s_meta[(cs / 2 - kb * 4) * 256 + (rs * 2 + (cs & 1) - mb * 256)];
+    }
+    reinterpret_cast<uint4*>(meta_tile)[tile * 128 + u] = *reinterpret_cast<const uint4*>(out);
   }
+  __syncthreads();
+  if (t < 64) reinterpret_cast<uint4*>(bits_tile)[tile * 64 + t] = reinterpret_cast<const uint4*>(s_out)[t];
 }
 
 // tile order -> dense {-1, 0, +1} * scale, fp16 row-major (m, k). Used by the Python-level
@@ -84,8 +106,13 @@ namespace ob {
 
 cudaError_t launch_relayout(const void* bits_ref, const void* meta_ref, int dialect, int64_t m, int64_t k,
                             void* bits_tile, void* meta_tile, cudaStream_t stream) {
+  // 16-byte accesses throughout; the reference's kernel asks the same of its A and E operands (128-bit alignment,
+  // csrc/kernel.h:19-21 of the reference)
+  if ((reinterpret_cast<uintptr_t>(bits_ref) | reinterpret_cast<uintptr_t>(meta_ref) | reinterpret_cast<uintptr_t>(bits_tile) |
+       reinterpret_cast<uintptr_t>(meta_tile)) & 15)
+    return cudaErrorMisalignedAddress;
   dim3 grid((unsigned)(k / 128), (unsigned)(m / 128));
-  ob_relayout_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(bits_ref),
+  ob_relayout_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(bits_ref),
                                                static_cast<const uint16_t*>(meta_ref), dialect, m, k,
                                                static_cast<uint32_t*>(bits_tile), static_cast<uint16_t*>(meta_tile));
   return cudaGetLastError();

@@ -147,3 +147,20 @@ def test_fp16_rounding_matches_numpy():
 
 def test_mask24_against_reference(golden):
     assert (oracle.mask24(golden["mask_dense"]) == golden["mask_mask"]).all()
+
+
+def test_gemm_against_the_references_own_host_gemm():
+    """The oracle's GEMM against the reference's host check GEMM itself -- the CUTLASS template its CLI instantiates
+    (tests/kernel_test.cu:441-456), compiled from the CUTLASS headers on this machine into oracle/_ref/ -- on the same
+    seeded operands: integer tokens, so the weighted checksum of the fp32 result must agree exactly."""
+    from oracle import build_ref
+    if build_ref.build() is None:
+        pytest.skip("no CUTLASS copy with host reference utilities on this machine")
+    m, n, k = 128, 64, 256
+    seconds, gflops, checksum = build_ref.run(m, n, k, seed=11)
+    A, B = build_ref.inputs(m, n, k, seed=11)
+    canon, signs, _ = oracle.compress(A)
+    c32, _ = oracle.gemm(oracle.pack_bits(signs), oracle.meta_reorder(canon, oracle.META_CUTLASS), oracle.META_CUTLASS, B, m)
+    weights = (np.arange(m * n) % 7 + 1).astype(np.float64)
+    assert float((c32.reshape(-1).astype(np.float64) * weights).sum()) == checksum
+    assert (c32 == A.astype(np.float32) @ B.astype(np.float32)).all()
