@@ -51,7 +51,7 @@ PUBLISHED = {512: 14.8383, 1024: 27.4138, 2048: 46.4786, 4096: 52.1011, 8192: 67
              25600: 69.9825}
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel on one GPU, from ncu
 # captures of exactly these workloads (bytes)
-MEASURED_TRAFFIC = {8192: 2.518e8}
+MEASURED_TRAFFIC = {8192: 2.518e8, 25600: 9.07e9}
 
 
 def load_peaks():

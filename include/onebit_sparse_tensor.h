@@ -44,7 +44,7 @@ enum { ONEBIT_META_PYTHON = 0,   /* onebit_sparse_mul/_semi_structured_conversio
        ONEBIT_META_CUTLASS = 1 };/* CUTLASS reorder_meta + ColumnMajorInterleaved<2> (csrc/threadblock.h:198-199) */
 enum { ONEBIT_OUT_F32 = 0, ONEBIT_OUT_F16 = 1 };
 enum { ONEBIT_DENSE_F16 = 0, ONEBIT_DENSE_BF16 = 1, ONEBIT_DENSE_I32 = 2 };
-enum { ONEBIT_KERNEL_AUTO = 0,    /* decode kernel for n <= 16 or n % 8 != 0, tensor-memory kernel otherwise */
+enum { ONEBIT_KERNEL_AUTO = 0,    /* few-token kernel for n <= 16 (n <= 32 up to 8192 rows) or n % 8 != 0, tile kernels otherwise */
        ONEBIT_KERNEL_PREFILL = 1, /* TMA + tcgen05.mma.sp kernel */
        ONEBIT_KERNEL_DECODE = 2,  /* split-K cluster kernel for few tokens */
        /* Flag, OR-ed into any of the above: the caller vouches that the packed weights of this call were

@@ -7,7 +7,7 @@ CSRC=$(PKG)/csrc
 NVCC=/usr/local/cuda/bin/nvcc
 NVCC_FLAGS=-gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 --expt-relaxed-constexpr -I$(ROOT)/include
 LIB_SRCS=$(CSRC)/api.cu $(CSRC)/pack.cu $(CSRC)/mask.cu $(CSRC)/relayout.cu $(CSRC)/gemm_simple.cu \
-         $(CSRC)/gemm_decode.cu $(CSRC)/gemm_decode_sm100.cu $(CSRC)/gemm_prefill_sm100.cu $(CSRC)/gemm_prefill2_sm100.cu $(CSRC)/gemm_prefill3_sm100.cu $(CSRC)/noalloc.cu $(CSRC)/host_pipeline.cu
+         $(CSRC)/gemm_decode.cu $(CSRC)/gemm_decode_sm100.cu $(CSRC)/gemm_prefill_sm100.cu $(CSRC)/gemm_prefill2_sm100.cu $(CSRC)/gemm_prefill3_sm100.cu $(CSRC)/gemm_prefill_splitk_sm100.cu $(CSRC)/noalloc.cu $(CSRC)/host_pipeline.cu
 
 kernel: share_lib
 	$(NVCC) $(NVCC_FLAGS) $(CSRC)/kernel_test.cu -o a.out -L$(PKG) -lonebitmul -Xlinker -rpath='$$ORIGIN/onebitsparsemul_b200'

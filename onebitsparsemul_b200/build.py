@@ -12,7 +12,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libonebitmul.so")
-SOURCES = ["api.cu", "pack.cu", "mask.cu", "relayout.cu", "gemm_simple.cu", "gemm_decode.cu", "gemm_decode_sm100.cu", "gemm_prefill_sm100.cu", "gemm_prefill2_sm100.cu", "gemm_prefill3_sm100.cu", "noalloc.cu", "host_pipeline.cu"]
+SOURCES = ["api.cu", "pack.cu", "mask.cu", "relayout.cu", "gemm_simple.cu", "gemm_decode.cu", "gemm_decode_sm100.cu", "gemm_prefill_sm100.cu", "gemm_prefill2_sm100.cu", "gemm_prefill3_sm100.cu", "gemm_prefill_splitk_sm100.cu", "noalloc.cu", "host_pipeline.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -127,8 +127,11 @@ int matmul_packed_impl(const void* bits_tile, const void* meta_tile, const void*
     return fail(ONEBIT_ERR_SHAPE, "tile-ordered GEMM needs m %% 128 == 0, k %% 128 == 0, n >= 1 (got m=%lld n=%lld k=%lld)",
                 (long long)m, (long long)n, (long long)k);
   if (out_type != OB_OUT_F32 && out_type != OB_OUT_F16) return fail(ONEBIT_ERR_ARG, "unknown output type %d", out_type);
+  // Up to 16 tokens, and up to 32 on matrices of at most 8192 rows (two passes of the few-token kernel still beat
+  // the tile kernels there: 7.6 against 12 us at 4096 x 4096, 19 against 23 us at 8192 x 8192; at 11008 rows the
+  // tile kernel fills the chip and wins, 14.5 against 20 us): the few-token kernel. More tokens: the tile kernels.
   if (kernel == ONEBIT_KERNEL_AUTO)
-    kernel = (n > 16 && ob::prefill_supported(m, n, k)) ? ONEBIT_KERNEL_PREFILL : ONEBIT_KERNEL_DECODE;
+    kernel = ((n > 32 || (n > 16 && m > 8192)) && ob::prefill_supported(m, n, k)) ? ONEBIT_KERNEL_PREFILL : ONEBIT_KERNEL_DECODE;
   cudaError_t e;
   if (kernel == ONEBIT_KERNEL_PREFILL) {
     if (!ob::prefill_supported(m, n, k))

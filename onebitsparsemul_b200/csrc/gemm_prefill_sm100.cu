@@ -327,6 +327,10 @@ cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tma
                                  const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
                                  void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
                                  cudaStream_t stream);
+int prefill_splitk_choose(int64_t tiles, int64_t kt);
+cudaError_t launch_gemm_prefill_splitk(const CUtensorMap* tmap, int S, const void* bits_tile, const void* meta_tile,
+                                       const void* scale, void* d, int64_t m, int64_t n, int64_t k, int out_type,
+                                       int* status, cudaStream_t stream);
 bool prefill3_supported(int64_t m, int64_t n, int64_t k, int out_type, const void* d, bool token_major);
 cudaError_t launch_gemm_prefill3(const CUtensorMap* tmap, bool token_major, const void* bits_tile, const void* meta_tile,
                                  const void* scale, const void* bias, void* d, void* const* extra_dst, int n_extra,
@@ -363,9 +367,9 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   // shared memory: the first version of this kernel, kept as the baseline of the profiling history),
   // 1121 / 1141 / 1221 (single CTA, operand in tensor memory: 128 tokens / 256 tokens / two stacked
   // weight tiles), 2 / 22 (CTA-pair kernel with one / two weight tiles per stage), 3 (persistent CTA-pair
-  // kernel), 1 (shape heuristic without the CTA-pair kernels).
+  // kernel), 4 (split-K cluster kernel), 1 (shape heuristic without the CTA-pair kernels).
   const int forced = forced_variant();
-  const int64_t row_tiles = m / BM;
+  const int64_t row_tiles = m / BM, kt_tiles = k / BK;
   const bool two = (m % 256 == 0);
   const int sms = sm_count();
   // The CTA-pair kernel (256 rows x 256 tokens per pair, each CTA staging half of the token tile) is
@@ -412,6 +416,11 @@ cudaError_t launch_gemm_prefill(const void* bits_tile, const void* meta_tile, co
   // spreads a small problem over the most SMs.
   if (n > 128 && row_tiles * ((n + 255) / 256) >= sms) return launch<1, 256, 1, true>(tmap, a, stream);
   if (two && (row_tiles / 2) * ((n + 127) / 128) >= sms) return launch<2, 128, 1, true>(tmap, a, stream);
+  // Too few output tiles to fill the chip: the same 128 x 128 pipeline with k cut over a cluster (variant 4 forces it;
+  // with one slice it is the plain single-CTA kernel).
+  const int64_t tiles = row_tiles * ((n + 127) / 128);
+  const int S = prefill_splitk_choose(tiles, kt_tiles);
+  if (forced == 4 || S > 1) return launch_gemm_prefill_splitk(&tmap, S, bits_tile, meta_tile, scale, d, m, n, k, out_type, status, stream);
   return launch<1, 128, 1, true>(tmap, a, stream);
 }
 

@@ -375,6 +375,61 @@ def test_every_kernel_variant_exact(variant):
     assert r.returncode == 0 and "variant ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+# ---- the split-K cluster form of the tensor-memory kernel (tens to hundreds of tokens on small outputs) -----------
+
+_SPLITK_CHILD = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1])
+import oracle
+from onebitsparsemul_b200 import _lib
+from tests import helpers
+lib = _lib.load()
+rng = np.random.default_rng(23)
+# 20 and 9 weight tiles along k (unequal slices for most splits), ragged token blocks, more than one token block
+for (m, n, k) in ((256, 136, 2560), (384, 40, 1152), (128, 264, 1024)):
+    dense, scale = helpers.make_weights(rng, m, k)
+    canon, signs, _ = oracle.compress(dense)
+    bits, meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, 0)
+    bt, mt = helpers.tile_order_from_canonical(canon, signs)
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    d_bt, d_mt, d_sc = t(bt), t(mt), t(scale)
+    B = helpers.make_tokens(rng, k, n, "int")
+    want, _ = oracle.gemm(bits, meta, 0, B, m)
+    d_b = t(B)
+    for out_dtype, code in ((torch.float32, _lib.OUT_F32), (torch.float16, _lib.OUT_F16)):
+        out = torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda")
+        _lib.check(lib.onebit_matmul_packed(d_bt.data_ptr(), d_mt.data_ptr(), None, d_b.data_ptr(), out.data_ptr(), m, n, k, code, _lib.KERNEL_PREFILL, None))
+        _lib.check(lib.onebit_check_device_status())
+        assert (out.cpu().numpy() == want.astype(out.cpu().numpy().dtype)).all(), (m, n, k, out_dtype)
+    B = helpers.make_tokens(rng, k, n)
+    want32, _ = oracle.gemm(bits, meta, 0, B, m, scale=scale)
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    _lib.check(lib.onebit_matmul_packed(d_bt.data_ptr(), d_mt.data_ptr(), d_sc.data_ptr(), t(B).data_ptr(), out.data_ptr(), m, n, k, _lib.OUT_F16, _lib.KERNEL_PREFILL, None))
+    _lib.check(lib.onebit_check_device_status())
+    ok, worst = helpers.row_tolerance_ok(out.cpu().numpy(), want32)
+    assert ok, (m, n, k, worst)
+print("split ok")
+"""
+
+
+@pytest.mark.parametrize("split", ["1", "2", "3", "4", "5", "8"])
+def test_split_k_cluster_kernel_exact(split):
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ONEBIT_PREFILL_VARIANT="4", ONEBIT_PREFILL_SPLIT=split)
+    r = subprocess.run([sys.executable, "-c", _SPLITK_CHILD, root], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "split ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("m,n,k", [(1024, 64, 4096), (4096, 128, 4096), (4096, 256, 4096), (4096, 32, 11008)])
+def test_mid_n_shapes_through_the_dispatcher(lib, m, n, k):
+    # few output tiles, long k: the dispatcher cuts k over a cluster; exact on integers, in tolerance otherwise
+    check_exact_and_tolerance(lib, Problem(m + n + k, m, k), n, _lib.KERNEL_AUTO)
+
+
 # ---- the persistent CTA-pair kernel walking several output tiles per cluster --------------------------------
 
 _PERSISTENT_CHILD = r"""
