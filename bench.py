@@ -155,10 +155,13 @@ class CpuSample:
         dense, self.scale = helpers.make_weights(rng, rows, size)
         canon, signs, _ = oracle.compress(dense)
         self.bits, self.meta = oracle.pack_bits(signs), oracle.meta_reorder(canon, oracle.META_CUTLASS)
+        # N(0,1) tokens: one 512-row block drawn, then repeated down the matrix (the values do not change the
+        # oracle's work, and drawing 6.5e8 normals would take longer than the GEMM sample)
+        block = rng.standard_normal((min(size, 512), size), dtype=np.float32).astype(np.float16)
         self.B = np.empty((size, size), np.float16)
-        for r0 in range(0, size, 1024):                      # N(0,1) tokens, drawn in slices to bound the temporaries
-            r1 = min(size, r0 + 1024)
-            self.B[r0:r1] = rng.standard_normal((r1 - r0, size), dtype=np.float32).astype(np.float16)
+        for r0 in range(0, size, block.shape[0]):
+            r1 = min(size, r0 + block.shape[0])
+            self.B[r0:r1] = block[:r1 - r0]
         # all host cores, whatever OMP_NUM_THREADS a launcher exported (torchrun sets it to 1)
         self.cores = len(os.sched_getaffinity(0))
 
@@ -178,7 +181,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = max(16, min(512, int(512 * (8192.0 / args.size) ** 2) // 16 * 16))     # about the same work per step at every size
+    rows = max(64, min(512, int(512 * (8192.0 / args.size) ** 2) // 64 * 64))     # about the same work per step at every size; whole 64-row groups (metadata shuffle)
     cpu = CpuSample(args.size, rows)
     vals = []
     for i in range(args.warmup + args.steps):

@@ -77,6 +77,8 @@ def compress(dense: np.ndarray, dtype_code: int | None = None):
 def meta_reorder(canon: np.ndarray, dialect: int) -> np.ndarray:
     canon = np.ascontiguousarray(canon, np.uint16)
     m, nc = canon.shape
+    if m % (64 if dialect == META_PYTHON else 32) != 0:
+        raise ValueError(f"{m} rows: the metadata shuffle works on whole groups of {64 if dialect == META_PYTHON else 32} rows")
     out = np.zeros((m, nc), np.uint16)
     lib().ob_oracle_meta_reorder(_p(canon), dialect, ctypes.c_int64(m), ctypes.c_int64(nc), _p(out))
     return out
@@ -85,6 +87,8 @@ def meta_reorder(canon: np.ndarray, dialect: int) -> np.ndarray:
 def meta_unreorder(meta: np.ndarray, dialect: int) -> np.ndarray:
     meta = np.ascontiguousarray(meta).view(np.uint16)
     m, nc = meta.shape
+    if m % (64 if dialect == META_PYTHON else 32) != 0:
+        raise ValueError(f"{m} rows: the metadata shuffle works on whole groups of {64 if dialect == META_PYTHON else 32} rows")
     out = np.zeros((m, nc), np.uint16)
     lib().ob_oracle_meta_unreorder(_p(meta), dialect, ctypes.c_int64(m), ctypes.c_int64(nc), _p(out))
     return out
