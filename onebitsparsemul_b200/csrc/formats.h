@@ -50,6 +50,21 @@ OB_HD void ob_meta_ref_position(int dialect, int64_t row, int64_t chunk, int64_t
   *c_out = c;
 }
 
+// The same permutation on coordinates inside one 128-row block (both row shuffles stay inside 64 / 32 rows, the
+// column swap inside a pair of chunks): unsigned arithmetic, for device code that works tile by tile.
+OB_HD void ob_meta_ref_position_local(int dialect, unsigned row, unsigned chunk, unsigned* r_out, unsigned* c_out) {
+  unsigned r;
+  if (dialect == OB_META_PYTHON) {
+    r = (row & ~63u) + (row & 1u) * 2 + ((row >> 2) & 1u) + ((row >> 1) & 1u) * 32 + ((row >> 3) & 7u) * 4;
+  } else {
+    r = (row & ~31u) + (row & 7u) * 4 + ((row >> 3) & 3u);
+  }
+  // the 2x2 swap exchanges the low bits of row and column when they differ
+  const unsigned x = (r ^ chunk) & 1u;
+  *r_out = r ^ x;
+  *c_out = chunk ^ x;
+}
+
 // Flat uint16 offset of canonical Meta[row][chunk] inside a reference-ordered metadata buffer of
 // an (m x k) matrix: column-major, interleaved by 2 columns (nchunks = k/16 is not needed).
 OB_HD int64_t ob_meta_ref_offset(int dialect, int64_t m, int64_t row, int64_t chunk) {

@@ -7,9 +7,10 @@
 //   * one CTA = one 128-row block of A x one slice of K. Weights arrive by bulk async copies in rounds of
 //     4 tiles (12 KiB) into a shared-memory ring, the whole first ring requested by one thread at kernel
 //     start;
-//   * 8 worker warps (thread = weight row, two groups of 4 warps taking alternate tiles) expand a tile's
-//     64 sign bits per row into 32 registers of fp16 +-1 pairs (one shift + one logic op per pair) and store
-//     them with tcgen05.st into a ring of tensor-memory slots; one thread copies the tile's metadata block
+//   * 8 worker warps (thread = weight row, two groups of 4 warps taking alternate pairs of tiles) expand a
+//     tile's 64 sign bits per row into 32 registers of fp16 +-1 pairs (one integer multiply by a power of two on
+//     the FMA pipe + one logic op on the ALU pipe per pair) and store them with tcgen05.st into a ring of
+//     tensor-memory slots, one wait and one hand-over per pair; one thread copies the tile's metadata block
 //     into tensor memory (tcgen05.cp) and issues 4 x tcgen05.mma.sp.kind::f16 (M = 128, N = 16, K = 32 dense)
 //     with the +-1 operand read from tensor memory. The K loop accumulates in tensor memory, so no partial
 //     sums of a CTA ever meet in shared memory, no warp reads token fragments, and the legacy mma.sp issue
@@ -105,6 +106,9 @@ struct FewTokArgs {
   void* d;
   int64_t m, n, k;
   int fresh_weights;    // 1: request no weights before the previous kernel of the stream has completed
+  uint32_t pow2[16];    // pow2[p] = 1 << (15 - p): a multiplication by a value the compiler does not know is an integer
+                        // multiply-add (FMA pipe), a shift by a constant is an ALU-pipe instruction like the logic
+                        // operation that follows it; the expansion is bound by the ALU pipe
 };
 
 // start-address field of a shared-memory matrix descriptor: bits 4-17 of the address. The mask matters: inside a
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   auto bar_wfull = [&](int s) { return bar0 + 8 * s; };                        // a round of weights has landed
   auto bar_wempty = [&](int s) { return bar0 + 8 * (kRing + s); };             // its MMAs are done: weights and tokens free
   auto bar_tfull = [&](int s) { return bar0 + 8 * (2 * kRing + s); };          // its tokens are staged (8 warps)
-  auto bar_afull = [&](int y) { return bar0 + 8 * (3 * kRing + y); };          // both operand slots of pair y written (8 warps)
+  auto bar_afull = [&](int y) { return bar0 + 8 * (3 * kRing + y); };          // both operand slots of pair y written (the 4 warps of group y)
   auto bar_aempty = [&](int y) { return bar0 + 8 * (3 * kRing + kPairs + y); };    // the MMAs reading pair y are done
   const uint32_t bar_acc = bar0 + 8 * (3 * kRing + 2 * kPairs);
   const uint32_t bar_recv = bar_acc + 8;                                       // every slice's sums for this CTA's rows have landed
@@ -199,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       const int npre = min(nrounds, kRing);
       for (int r = 0; r < npre; ++r) issue(r);
       for (int s = 0; s < kRing; ++s) { mbar_init(bar_wempty(s), 1); mbar_init(bar_tfull(s), kWorkers / 32); }
-      for (int y = 0; y < kPairs; ++y) { mbar_init(bar_afull(y), kWorkers / 32); mbar_init(bar_aempty(y), 1); }
+      for (int y = 0; y < kPairs; ++y) { mbar_init(bar_afull(y), kWorkers / 64); mbar_init(bar_aempty(y), 1); }
       mbar_init(bar_acc, 1);
       mbar_init(bar_recv, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -280,11 +284,21 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
 #define WORKER_WAIT(bar, par, code) mbar_wait(bar, par, budget, &g_fewtok_status, code)
   if (warp < 8) {
     // ---------------- workers: stage tokens, expand sign bits into tensor memory ----------------
+    // Group g (warps 4g .. 4g+3, one 32-row quadrant each) owns pair g of every round: tiles 2g and 2g + 1 and the
+    // operand slots of the same numbers. A warp expands both tiles of its pair back to back, waits once for the two
+    // tensor-memory stores and arrives once; the other group works on the other pair at the same time.
     const int q = warp & 3, grp = warp >> 2;
     const int row = q * 32 + lane;
+    const uint32_t a_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 64 * grp);
+    // one word of 32 sign bits -> 16 registers of two fp16 +-1 each: bit p to bit 15, bit p + 16 to bit 31
+    auto expand_word = [&](uint32_t w, uint32_t* v) {
+#pragma unroll
+      for (int p = 0; p < 15; ++p) v[p] = ((w * a.pow2[p]) & 0x80008000u) ^ 0xBC00BC00u;
+      v[15] = (w & 0x80008000u) ^ 0xBC00BC00u;
+    };
+    int s = 0;
 #pragma unroll 1
     for (int r = 0; r < nrounds; ++r) {
-      const int s = r % kRing;
       OB_TRACE_ROUND(12, r);
       if (r >= kRing) WORKER_WAIT(bar_wempty(s), ((r / kRing) - 1) & 1, 201);
       OB_TRACE_ROUND(13, r);
@@ -298,31 +312,32 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       OB_TRACE_ROUND(15, r);
       if (r == 0) OB_TRACE_EV(3);
       const int nt = min(KL, T - r * KL);
-#pragma unroll 1
-      for (int pp = 0; 2 * pp < nt; ++pp) {
-        // pair P of the slice = tiles 2P (first group of warps) and 2P + 1 (second group); its two operand slots
-        // are handed back by one commit and handed over by one barrier
-        const int P = r * (KL / 2) + pp, y = P & 1, j = 2 * pp + grp;
-        // Every warp waits for the pair's slots, also one whose group has no tile in the last pair of an odd slice:
-        // arriving below without this wait could complete the PREVIOUS use of the barrier while a slower warp has
-        // not yet written its quadrant, and the MMAs would read a stale operand.
-        WORKER_WAIT(bar_aempty(y), ((P >> 1) & 1) ^ 1, 203);
+      if (2 * grp < nt) {
+        const uint8_t* sw = wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + 2 * grp * OB_TILE_BITS_BYTES + row * 8;
+        const bool two = 2 * grp + 1 < nt;                    // an odd slice ends with half a pair
+        const uint2 w0 = *reinterpret_cast<const uint2*>(sw);
+        uint2 w1 = make_uint2(0, 0);
+        if (two) w1 = *reinterpret_cast<const uint2*>(sw + OB_TILE_BITS_BYTES);
+        OB_TRACE_TILE(2, r * KL + 2 * grp);
+        uint32_t v[32];
+        expand_word(w0.x, v);                                 // before the wait: only the store needs the slot
+        expand_word(w0.y, v + 16);
+        WORKER_WAIT(bar_aempty(grp), (r & 1) ^ 1, 203);       // the MMAs that read this pair of slots a round ago are done
         __syncwarp();        // the tcgen05 instructions below are .sync.aligned: no lane may still be in the wait loop
-        if (j < nt) {
-          const int t = r * KL + j, x = t & (kASlots - 1);
-          OB_TRACE_TILE(2, t);
-          const uint2 w = *reinterpret_cast<const uint2*>(wring + s * L::kRoundWeights + KL * OB_TILE_META_BYTES + j * OB_TILE_BITS_BYTES + row * 8);
-          uint32_t v[32];
-#pragma unroll
-          for (int p = 0; p < 16; ++p) { v[p] = expand_pair(w.x, p); v[16 + p] = expand_pair(w.y, p); }
-          tcgen05_fence_after();
-          tcgen05_st_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 32 * x), v);
-          tcgen05_fence_before();
-          OB_TRACE_TILE(3, t);
+        tcgen05_fence_after();
+        tcgen05_st_32x32b_x32_nowait(a_col, v);
+        if (two) {
+          expand_word(w1.x, v);
+          expand_word(w1.y, v + 16);
+          tcgen05_st_32x32b_x32_nowait(a_col + 32, v);
         }
+        tcgen05_wait_st();
+        tcgen05_fence_before();
+        OB_TRACE_TILE(3, r * KL + 2 * grp);
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_afull(y));             // also without a tile: the count is 8 warps
+        if (lane == 0) mbar_arrive(bar_afull(grp));
       }
+      if (++s == kRing) s = 0;
     }
     OB_TRACE_EV(4);
   } else if (warp == kProdWarp) {
@@ -551,7 +566,8 @@ cudaError_t launch_gemm_fewtok(const void* bits_tile, const void* meta_tile, con
                                bool fresh_weights, cudaStream_t stream) {
   FewTokArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(b), d, m, n, k,
-               fresh_weights ? 1 : 0};
+               fresh_weights ? 1 : 0, {}};
+  for (int p = 0; p < 16; ++p) a.pow2[p] = 1u << (15 - p);
   return token_major ? dispatch<true>(a, out_type, stream) : dispatch<false>(a, out_type, stream);
 }
 

@@ -5,21 +5,14 @@
 #pragma once
 #include <stdint.h>
 
-// bit t set = weight t of the group is kept
+// bit t set = weight t of the group is kept. The keys |w| * 4 + t are distinct, so that six comparisons rank the
+// group: weight t is kept when at least two keys are smaller than its own.
 __device__ __forceinline__ unsigned ob_keep_mask4(const uint16_t* w) {
-  unsigned keep = 0;
-#pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const unsigned at = w[t] & 0x7fffu;       // |w| of an fp16 orders like its low 15 bits; NaN last
-    int rank = 0;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const unsigned au = w[u] & 0x7fffu;
-      rank += (au < at) || (au == at && u < t);
-    }
-    keep |= (rank >= 2 ? 1u : 0u) << t;
-  }
-  return keep;
+  const unsigned k0 = (w[0] & 0x7fffu) * 4u, k1 = (w[1] & 0x7fffu) * 4u + 1u;   // |w| of an fp16 orders like its low 15 bits; NaN last
+  const unsigned k2 = (w[2] & 0x7fffu) * 4u + 2u, k3 = (w[3] & 0x7fffu) * 4u + 3u;
+  const int c01 = k0 < k1, c02 = k0 < k2, c03 = k0 < k3, c12 = k1 < k2, c13 = k1 < k3, c23 = k2 < k3;
+  const int r0 = 3 - c01 - c02 - c03, r1 = c01 + 2 - c12 - c13, r2 = c02 + c12 + 1 - c23, r3 = c03 + c13 + c23;
+  return (r0 >= 2 ? 1u : 0u) | (r1 >= 2 ? 2u : 0u) | (r2 >= 2 ? 4u : 0u) | (r3 >= 2 ? 8u : 0u);
 }
 
 // what the reference's `weight * mask` leaves of a dropped weight: a signed zero, a NaN stays a NaN

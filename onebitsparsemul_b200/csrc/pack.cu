@@ -7,9 +7,10 @@
 //
 // One CTA owns one 128-row x 128-column tile. A warp owns 32 rows of one 16-column chunk, lane =
 // row, so that the column-major-in-m sign bitfield of the reference falls out of warp ballots and
-// the 4 nibbles of a chunk are one lane's private work. Everything is staged in shared memory and
-// leaves the SM as 16-byte stores. HBM-bound: 2 bytes read and at most ~0.6 byte written per dense
-// weight.
+// the 4 nibbles of a chunk are one lane's private work. 16-bit weights enter the SM as coalesced 16-byte
+// loads (a quarter-warp reads 128 contiguous bytes of a row) into a padded shared-memory tile, from which a
+// lane then takes its 32 bytes without bank conflicts; everything leaves the SM as 16-byte stores.
+// HBM-bound: 2 bytes read and at most ~0.6 byte written per dense weight.
 //
 // Fused form (fp16 only): the 2:4 magnitude mask of mask_creator (_semi_structured_conversions.py:286-314)
 // is applied to the 16 values a lane has just loaded, before they are encoded, so that the whole of
@@ -66,10 +67,31 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
   __shared__ __align__(16) uint32_t s_bits_ref[64 * 4];    // [q local][32-row group]
   __shared__ __align__(16) uint16_t s_meta_ref[4 * 256];   // [chunk pair][shuffled row][2]
 
+  // 16-bit weights: the dense tile itself, rows 272 bytes apart (lanes of a quarter-warp, one row each, then hit
+  // disjoint banks with their 16-byte accesses)
+  constexpr bool kStaged = sizeof(T) == 2;
+  constexpr int kRowStride = 136;                            // uint16 per staged row
+  __shared__ __align__(16) uint16_t s_dense[kStaged ? 128 * kRowStride : 8];
+
   const int64_t kb = blockIdx.x, mb = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t nchunks = a.k / 16;
 
+  if constexpr (kStaged) {
+    uint4 stage[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + 256 * i, r = idx >> 4, c8 = idx & 15;   // row of the tile, 8-value piece of the row
+      const int64_t row = mb * 128 + r, col = kb * 128 + c8 * 8;
+      stage[i] = (row < a.m && col < a.k) ? __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(a.dense) + row * a.k + col))
+                                          : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + 256 * i, r = idx >> 4, c8 = idx & 15;
+      *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c8 * 8]) = stage[i];
+    }
+  }
   s_bits_tile[threadIdx.x] = 0;
   s_bits_ref[threadIdx.x] = 0;
   for (int i = threadIdx.x; i < 1024; i += 256) { s_meta_tile[i] = 0; s_meta_ref[i] = 0; }
@@ -82,7 +104,11 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
     const bool valid = row < a.m && chunk < nchunks;
 
     T e[16];
-    if (valid) {
+    if constexpr (kStaged) {
+      // rows and columns beyond the matrix were staged as zeros
+      *reinterpret_cast<uint4*>(&e[0]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16]);
+      *reinterpret_cast<uint4*>(&e[8]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16 + 8]);
+    } else if (valid) {
       const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.dense) + row * a.k + chunk * 16);
 #pragma unroll
       for (int v = 0; v < 16 / kElemsPer16B; ++v) {
@@ -103,10 +129,9 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
           for (int t = 0; t < 4; ++t)
             if (!((keep >> t) & 1u)) e[4 * g + t] = ob_dropped_value(e[4 * g + t]);
         }
-        if (a.masked) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.masked) + row * a.k + chunk * 16);
-          dst[0] = *reinterpret_cast<uint4*>(&e[0]);
-          dst[1] = *reinterpret_cast<uint4*>(&e[8]);
+        if (a.masked) {                                 // back into the staged tile; stored row-wise at the end
+          *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16]) = *reinterpret_cast<uint4*>(&e[0]);
+          *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16 + 8]) = *reinterpret_cast<uint4*>(&e[8]);
         }
       }
     }
@@ -153,15 +178,26 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
     }
     // reference-ordered metadata: destination stays inside this tile's 4 chunk pairs x 128 rows
     {
-      int64_t rs, cs;                                                   // shuffled row and column
-      ob_meta_ref_position(a.dialect, row, chunk, &rs, &cs);
-      s_meta_ref[(cs / 2 - kb * 4) * 256 + (rs * 2 + (cs & 1) - mb * 256)] = (uint16_t)meta;
+      unsigned rs, cs;                                                  // shuffled row and column inside the tile
+      ob_meta_ref_position_local(a.dialect, (unsigned)r, (unsigned)c, &rs, &cs);
+      s_meta_ref[(cs >> 1) * 256 + rs * 2 + (cs & 1)] = (uint16_t)meta;
     }
   }
   __syncthreads();
 
   const int t = threadIdx.x;
   const bool full = (mb * 128 + 128 <= a.m) && (kb * 128 + 128 <= a.k);
+  if constexpr (DT == OB_DENSE_F16) {
+    if (a.apply_mask && a.masked) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = t + 256 * i, r = idx >> 4, c8 = idx & 15;
+        const int64_t row = mb * 128 + r, col = kb * 128 + c8 * 8;
+        if (row < a.m && col < a.k)
+          *reinterpret_cast<uint4*>(static_cast<T*>(a.masked) + row * a.k + col) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c8 * 8]);
+      }
+    }
+  }
   if (a.meta_tile && full && t < 128)
     reinterpret_cast<uint4*>(a.meta_tile)[(mb * (a.k / 128) + kb) * 128 + t] = reinterpret_cast<uint4*>(s_meta_tile)[t];
   if (a.bits_tile && full && t >= 128 && t < 192)

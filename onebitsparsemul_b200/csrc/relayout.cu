@@ -4,7 +4,7 @@
 // one of two shuffled orders (csrc/kernel.h:13-18, csrc/threadblock.h:198-199,
 // onebit_sparse_mul/_semi_structured_conversions.py:21-48). The GEMM kernels of this library read
 // 128x128 tiles whose sign bits are row-major in k and whose metadata is laid out for tensor
-// memory. This kernel is the bit transpose between the two; one CTA per tile, HBM-bound
+// memory. This kernel is the bit transpose between the two; one CTA per four vertically adjacent tiles, HBM-bound
 // (3/16 byte read and written per dense weight). The operands must be 16-byte aligned.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -14,26 +14,38 @@
 
 namespace {
 
-// One CTA per 128 x 128 tile. Everything enters and leaves the SM as 16-byte accesses: in the reference orders the
-// tile's sign bits are 64 segments of 16 bytes (128 rows of one bitfield column each) and its metadata is 4 runs of
-// 512 bytes (one per pair of 16-column chunks: the row shuffles of both dialects stay inside a 128-row block);
-// both are staged in shared memory, permuted there, and stored in tile order.
+// One CTA per column of kRB vertically adjacent 128 x 128 tiles. Everything enters and leaves the SM as 16-byte
+// accesses: in the reference orders the sign bits of such a column are 64 segments of 16 * kRB bytes (128 * kRB rows of
+// one bitfield column each) and its metadata is 4 runs of 512 * kRB bytes (one per pair of 16-column chunks: the row
+// shuffles of both dialects stay inside a 128-row block). With kRB = 4 a segment is two whole 32-byte sectors and a
+// CTA has 12 KiB of loads in flight; everything is requested before anything is used, staged in shared memory,
+// permuted there, and stored in tile order (3 KiB contiguous per tile).
+constexpr int kRB = 4;
+
 __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restrict__ bits_ref,
                                                           const uint16_t* __restrict__ meta_ref, int dialect,
                                                           int64_t m, int64_t k, uint32_t* __restrict__ bits_tile,
                                                           uint16_t* __restrict__ meta_tile) {
-  __shared__ __align__(16) uint32_t s_bits[64 * 4];        // [kept value of the tile row][32-row group]
-  __shared__ __align__(16) uint16_t s_meta[4 * 256];       // [chunk pair][shuffled row][2]
-  __shared__ __align__(16) uint32_t s_out[256];            // the tile's sign block in tile order
-  const int64_t kb = blockIdx.x, mb = blockIdx.y;
+  __shared__ __align__(16) uint32_t s_bits[64 * kRB * 4];  // [kept value of the tile row][row block][32-row group]
+  __shared__ __align__(16) uint16_t s_meta[4 * kRB * 256]; // [chunk pair][row block][shuffled row][2]
+  __shared__ __align__(16) uint32_t s_out[kRB * 256];      // [row block] the tile's sign block in tile order
+  const int64_t kb = blockIdx.x, mb0 = (int64_t)blockIdx.y * kRB;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-  const int64_t tile = mb * (k / 128) + kb;
+  const int nrb = (int)min((int64_t)kRB, m / 128 - mb0);   // row blocks of this column that exist
 
-  if (t < 64) {
-    reinterpret_cast<uint4*>(s_bits)[t] = __ldg(reinterpret_cast<const uint4*>(bits_ref + ((kb * 64 + t) * m + mb * 128) / 8));
-  } else if (t < 192) {
-    const int pair = (t - 64) >> 5, j = (t - 64) & 31;     // 512 bytes per pair = 32 x 16 bytes
-    reinterpret_cast<uint4*>(s_meta)[t - 64] = __ldg(reinterpret_cast<const uint4*>(meta_ref + (kb * 4 + pair) * 2 * m + mb * 256 + j * 8));
+  {
+    const int q = t / kRB, rb = t % kRB;                   // 64 segments x kRB pieces of 16 bytes
+    uint4 vb = make_uint4(0, 0, 0, 0), vm[2];
+    if (rb < nrb) vb = __ldg(reinterpret_cast<const uint4*>(bits_ref + ((kb * 64 + q) * m + (mb0 + rb) * 128) / 8));
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = t + 256 * i, pair = idx / (kRB * 32), rem = idx % (kRB * 32);   // 4 runs x kRB * 32 pieces
+      vm[i] = make_uint4(0, 0, 0, 0);
+      if (rem / 32 < nrb) vm[i] = __ldg(reinterpret_cast<const uint4*>(meta_ref + (kb * 4 + pair) * 2 * m + mb0 * 256 + rem * 8));
+    }
+    reinterpret_cast<uint4*>(s_bits)[t] = vb;
+    reinterpret_cast<uint4*>(s_meta)[t] = vm[0];
+    reinterpret_cast<uint4*>(s_meta)[t + 256] = vm[1];
   }
   __syncthreads();
 
@@ -42,31 +54,36 @@ __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restr
   {
     const int rg = warp & 3, half = warp >> 2;
     const int q_local = half * 32 + 2 * (lane & 15) + (lane >> 4);
-    const uint32_t w = s_bits[q_local * 4 + rg];
-    uint32_t mine = 0;
+    for (int rb = 0; rb < nrb; ++rb) {
+      const uint32_t w = s_bits[(q_local * kRB + rb) * 4 + rg];
+      uint32_t mine = 0;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const uint32_t b = __ballot_sync(0xffffffffu, (w >> j) & 1u);
-      if (lane == j) mine = b;
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t b = __ballot_sync(0xffffffffu, (w >> j) & 1u);
+        if (lane == j) mine = b;
+      }
+      s_out[rb * 256 + (rg * 32 + lane) * 2 + half] = mine;
     }
-    s_out[(rg * 32 + lane) * 2 + half] = mine;
   }
-  // metadata: thread u < 128 assembles lane u of the tile block (8 words: chunk pairs c2 = 0..3, rows r and r + 8)
-  if (t < 128) {
-    const int u = t, r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4;
+  // metadata: thread u < 128 of each half of the CTA assembles lane u of a tile block (8 words: chunk pairs
+  // c2 = 0..3, rows r and r + 8); the two halves work on two row blocks at a time
+  for (int rb = t >> 7; rb < nrb; rb += 2) {
+    const unsigned u = t & 127, r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4;
     __align__(16) uint16_t out[8];
 #pragma unroll
-    for (int wd = 0; wd < 8; ++wd) {
-      const int c2 = wd >> 1, r1 = wd & 1;
-      const int64_t row = mb * 128 + r0 + 8 * r1 + 16 * r2, chunk = kb * 8 + 2 * c2 + c1;
-      int64_t rs, cs;
-      ob_meta_ref_position(dialect, row, chunk, &rs, &cs);
-      out[wd] = s_meta[(cs / 2 - kb * 4) * 256 + (rs * 2 + (cs & 1) - mb * 256)];
+    for (unsigned wd = 0; wd < 8; ++wd) {
+      const unsigned c2 = wd >> 1, r1 = wd & 1;
+      unsigned rs, cs;
+      ob_meta_ref_position_local(dialect, r0 + 8 * r1 + 16 * r2, 2 * c2 + c1, &rs, &cs);
+      out[wd] = s_meta[((cs >> 1) * kRB + rb) * 256 + rs * 2 + (cs & 1)];
     }
-    reinterpret_cast<uint4*>(meta_tile)[tile * 128 + u] = *reinterpret_cast<const uint4*>(out);
+    reinterpret_cast<uint4*>(meta_tile)[((mb0 + rb) * (k / 128) + kb) * 128 + u] = *reinterpret_cast<const uint4*>(out);
   }
   __syncthreads();
-  if (t < 64) reinterpret_cast<uint4*>(bits_tile)[tile * 64 + t] = reinterpret_cast<const uint4*>(s_out)[t];
+  {
+    const int rb = t >> 6, i = t & 63;
+    if (rb < nrb) reinterpret_cast<uint4*>(bits_tile)[((mb0 + rb) * (k / 128) + kb) * 64 + i] = reinterpret_cast<const uint4*>(s_out)[t];
+  }
 }
 
 // tile order -> dense {-1, 0, +1} * scale, fp16 row-major (m, k). Used by the Python-level
@@ -111,7 +128,7 @@ cudaError_t launch_relayout(const void* bits_ref, const void* meta_ref, int dial
   if ((reinterpret_cast<uintptr_t>(bits_ref) | reinterpret_cast<uintptr_t>(meta_ref) | reinterpret_cast<uintptr_t>(bits_tile) |
        reinterpret_cast<uintptr_t>(meta_tile)) & 15)
     return cudaErrorMisalignedAddress;
-  dim3 grid((unsigned)(k / 128), (unsigned)(m / 128));
+  dim3 grid((unsigned)(k / 128), (unsigned)((m / 128 + kRB - 1) / kRB));
   ob_relayout_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(bits_ref),
                                                static_cast<const uint16_t*>(meta_ref), dialect, m, k,
                                                static_cast<uint32_t*>(bits_tile), static_cast<uint16_t*>(meta_tile));
