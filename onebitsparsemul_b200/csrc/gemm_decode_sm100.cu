@@ -77,6 +77,7 @@ constexpr int kPairs = kASlots / 2;      // slots are handed over in pairs of co
 static_assert(kASlots == 4 && KL % 2 == 0, "the slot ring is indexed with masks; a round is whole pairs");
 static_assert(kTmemA + 32 * kASlots <= kTmemCols && kTmemE + 4 * kASlots <= kTmemA && 16 * kAccs <= kTmemE, "tensor memory plan");
 constexpr int kProdWarp = 8, kMmaWarp = 9;   // weight stream; tensor-memory allocation and MMA issue
+constexpr uint32_t kPollNs = 2000;      // a poll of a barrier may sleep this long inside the instruction (it wakes when the phase completes)
 constexpr int kMinSmem = 78 * 1024;      // at most two CTAs per SM, whatever the configuration needs
 
 // NG = groups of 8 token columns per pass (the MMA is always N = 16; with NG = 1 both halves read the same tokens)
@@ -219,52 +220,58 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   // tokens of one round: kPieces 16-byte pieces per worker, fetched into registers, stored as core matrices.
   //   K-major source: piece = 8 k values of token j          -> [tile][j / 8][k chunk][j % 8]
   //   N-major source: piece = 8 tokens (group ng) of k row kk -> [tile][ng][kk]          (16 bytes each)
+  // Everything that does not depend on the round is worked out once: the source of the piece in the slice's first
+  // round (it then moves on by a fixed stride per round), its place inside a round's staging area, the tile of the
+  // round it belongs to (a slice's last round may be short) and whether its tokens exist at all.
+  uint32_t tsrc[kPieces];                                     // element offset from a.b (the launcher checks n * k < 2^31)
+  uint32_t tplace[kPieces];                                   // bits 0-23: byte offset in the staging area, 24-31: tile
+#pragma unroll
+  for (int i = 0; i < kPieces; ++i) {
+    const int idx = tid + kWorkers * i;
+    if (kmajor) {
+      const int j = idx % NP, c = idx / NP;                   // token, 8-k chunk of the round (16 chunks per tile)
+      const int tile = (j < nvalid) ? (c >> 4) : KL;          // KL = never
+      tsrc[i] = (uint32_t)((n0 + j) * a.k + (int64_t)tile_begin * OB_TILE_K + c * 8);
+      tplace[i] = (uint32_t)((c >> 4) * L::kTileTokens + (j >> 3) * 2048 + (c & 15) * 128 + (j & 7) * 16) | ((uint32_t)tile << 24);
+    } else {
+      const int kk = idx / NG, ng = idx % NG;                 // k row of the round, token group
+      const int tile = (8 * ng < nvalid) ? (kk >> 7) : KL;
+      tsrc[i] = (uint32_t)(((int64_t)tile_begin * OB_TILE_K + kk) * a.n + n0 + 8 * ng);
+      tplace[i] = (uint32_t)((kk >> 7) * L::kTileTokens + ng * 2048 + (kk & 127) * 16) | ((uint32_t)tile << 24);
+    }
+  }
+  const uint32_t tstride = (uint32_t)(KL * OB_TILE_K * (kmajor ? 1 : a.n));   // elements from one round to the next
   auto fetch_tokens = [&](int r, uint4 (&tv)[kPieces]) {
     const int ntile = min(KL, T - r * KL);
-    const int64_t k0 = (int64_t)(tile_begin + r * KL) * OB_TILE_K;
 #pragma unroll
     for (int i = 0; i < kPieces; ++i) {
       tv[i] = make_uint4(0, 0, 0, 0);
-      const int idx = tid + kWorkers * i;
-      if (kmajor) {
-        const int j = idx % NP, c = idx / NP;                 // token, 8-k chunk of the round (64 chunks)
-        if (j < nvalid && (c >> 4) < ntile) tv[i] = __ldg(reinterpret_cast<const uint4*>(a.b + (n0 + j) * a.k + k0 + c * 8));
-      } else {
-        const int kk = idx / NG, ng = idx % NG;               // k row of the round, token group
-        if ((kk >> 7) < ntile && 8 * ng < nvalid) {
-          const __half* src = a.b + (k0 + kk) * a.n + n0 + 8 * ng;
-          if (vec_rows) {
-            tv[i] = __ldg(reinterpret_cast<const uint4*>(src));
-          } else if (quad_rows) {
-            uint2* h4 = reinterpret_cast<uint2*>(&tv[i]);     // n % 4 == 0: whole groups of four tokens
-            h4[0] = __ldg(reinterpret_cast<const uint2*>(src));
-            if (8 * ng + 4 < nvalid) h4[1] = __ldg(reinterpret_cast<const uint2*>(src + 4));
-          } else {
-            __half* h = reinterpret_cast<__half*>(&tv[i]);
+      if ((int)(tplace[i] >> 24) < ntile) {
+        const __half* src = a.b + tsrc[i];
+        if (kmajor || vec_rows) {
+          tv[i] = __ldg(reinterpret_cast<const uint4*>(src));
+        } else if (quad_rows) {
+          const int ng = (tid + kWorkers * i) % NG;
+          uint2* h4 = reinterpret_cast<uint2*>(&tv[i]);       // n % 4 == 0: whole groups of four tokens
+          h4[0] = __ldg(reinterpret_cast<const uint2*>(src));
+          if (8 * ng + 4 < nvalid) h4[1] = __ldg(reinterpret_cast<const uint2*>(src + 4));
+        } else {
+          const int ng = (tid + kWorkers * i) % NG;
+          __half* h = reinterpret_cast<__half*>(&tv[i]);
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj)
-              if (8 * ng + jj < nvalid) h[jj] = src[jj];
-          }
+          for (int jj = 0; jj < 8; ++jj)
+            if (8 * ng + jj < nvalid) h[jj] = src[jj];
         }
       }
+      tsrc[i] += tstride;
     }
   };
   auto store_tokens = [&](int r, const uint4 (&tv)[kPieces]) {
     const int ntile = min(KL, T - r * KL);
     uint8_t* sb = tring + (r % kRing) * L::kRoundTokens;
 #pragma unroll
-    for (int i = 0; i < kPieces; ++i) {
-      const int idx = tid + kWorkers * i;
-      if (kmajor) {
-        const int j = idx % NP, c = idx / NP;
-        if (j < nvalid && (c >> 4) < ntile)
-          *reinterpret_cast<uint4*>(sb + (c >> 4) * L::kTileTokens + (j >> 3) * 2048 + (c & 15) * 128 + (j & 7) * 16) = tv[i];
-      } else {
-        const int kk = idx / NG, ng = idx % NG;
-        if ((kk >> 7) < ntile && 8 * ng < nvalid)
-          *reinterpret_cast<uint4*>(sb + (kk >> 7) * L::kTileTokens + ng * 2048 + (kk & 127) * 16) = tv[i];
-      }
-    }
+    for (int i = 0; i < kPieces; ++i)
+      if ((int)(tplace[i] >> 24) < ntile) *reinterpret_cast<uint4*>(sb + (tplace[i] & 0xFFFFFFu)) = tv[i];
   };
 
   uint4 tv[kPieces];
@@ -281,7 +288,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   const uint32_t tmem_base = *tmem_slot_gen;
   OB_TRACE_EV(2);
 
-#define WORKER_WAIT(bar, par, code) mbar_wait(bar, par, budget, &g_fewtok_status, code)
+#define WORKER_WAIT(bar, par, code) mbar_wait_sleepy(bar, par, kPollNs, budget, &g_fewtok_status, code)
   if (warp < 8) {
     // ---------------- workers: stage tokens, expand sign bits into tensor memory ----------------
     // Group g (warps 4g .. 4g+3, one 32-row quadrant each) owns pair g of every round: tiles 2g and 2g + 1 and the
@@ -344,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     // ---------------- weight stream: refill a slot once its round has been multiplied ----------------
     if (lane == 0) {
       for (int r = kRing; r < nrounds; ++r) {
-        mbar_wait(bar_wempty(r % kRing), ((r / kRing) - 1) & 1, budget, &g_fewtok_status, 204);
+        mbar_wait_sleepy(bar_wempty(r % kRing), ((r / kRing) - 1) & 1, kPollNs, budget, &g_fewtok_status, 204);
         issue(r);
       }
     }
@@ -369,13 +376,13 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
 #pragma unroll 1
       for (int r = 0; r < nrounds; ++r) {
         const int nt = min(KL, T - r * KL);
-        mbar_wait(bar_tfull(s), rph, budget, &g_fewtok_status, 205);
-        mbar_wait(bar_wfull(s), rph, budget, &g_fewtok_status, 206);
+        mbar_wait_sleepy(bar_tfull(s), rph, kPollNs, budget, &g_fewtok_status, 205);
+        mbar_wait_sleepy(bar_wfull(s), rph, kPollNs, budget, &g_fewtok_status, 206);
 #pragma unroll 1
         for (int pp = 0; 2 * pp < nt; ++pp) {
           const int P = r * (KL / 2) + pp, y = P & 1;
           OB_TRACE_TILE(11, 2 * P);
-          mbar_wait(bar_afull(y), (P >> 1) & 1, budget, &g_fewtok_status, 207);
+          mbar_wait_sleepy(bar_afull(y), (P >> 1) & 1, kPollNs, budget, &g_fewtok_status, 207);
           OB_TRACE_TILE(4, 2 * P);
           tcgen05_fence_after();
 #pragma unroll
@@ -568,6 +575,7 @@ cudaError_t launch_gemm_fewtok(const void* bits_tile, const void* meta_tile, con
                static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(b), d, m, n, k,
                fresh_weights ? 1 : 0, {}};
   for (int p = 0; p < 16; ++p) a.pow2[p] = 1u << (15 - p);
+  if (k * (n > 1 ? n : 1) >= (int64_t)1 << 31) return cudaErrorInvalidValue;   // token offsets are 32-bit in the kernel
   return token_major ? dispatch<true>(a, out_type, stream) : dispatch<false>(a, out_type, stream);
 }
 

@@ -28,6 +28,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep inside the instruction until the phase
+// completes or the time is over, instead of coming back at once to spin in the issue slots of its neighbours.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
 // Bounded wait. `budget` is this thread's remaining patience in SM clock cycles; once a wait has
 // run out the thread stops waiting for anything (budget 0), records `code` and lets the kernel
 // drain. The clock is read only every 64 polls: the poll itself is the hot path.
@@ -38,6 +49,21 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, long lo
   unsigned polls = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 63u) == 0 && clock64() - start > budget) {
+      budget = 0;
+      atomicCAS(status, 0, code);
+      return;
+    }
+  }
+}
+
+// Bounded wait whose polls sleep up to `ns` nanoseconds each (see mbar_try_wait_hint); the clock is read every 16 polls.
+__device__ __forceinline__ void mbar_wait_sleepy(uint32_t bar, uint32_t parity, uint32_t ns, long long& budget, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return;
+  if (budget == 0) return;
+  const long long start = clock64();
+  unsigned polls = 0;
+  while (!mbar_try_wait_hint(bar, parity, ns)) {
+    if ((++polls & 15u) == 0 && clock64() - start > budget) {
       budget = 0;
       atomicCAS(status, 0, code);
       return;
