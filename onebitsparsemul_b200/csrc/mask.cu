@@ -8,6 +8,7 @@
 
 #include "kernels.h"
 #include "mask24.h"
+#include "pack16.h"
 
 namespace {
 
@@ -16,20 +17,23 @@ __global__ void __launch_bounds__(256) ob_mask24_kernel(const uint4* __restrict_
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= vecs) return;
   uint4 v = __ldg(dense + i);
-  uint16_t* w = reinterpret_cast<uint16_t*>(&v);
-  const unsigned keep = ob_keep_mask4(w) | (ob_keep_mask4(w + 4) << 4);
+  uint32_t k0, k1, k2, k3;                                  // bit 15 / 31: the weight in that half stays
+  ob_keep_group2(v.x, v.y, k0, k1);
+  ob_keep_group2(v.z, v.w, k2, k3);
   if (mask) {
-    uint2 mk;
-    uint8_t* mb = reinterpret_cast<uint8_t*>(&mk);
-#pragma unroll
-    for (int t = 0; t < 8; ++t) mb[t] = (keep >> t) & 1u;
-    mask[i] = mk;
+    // one byte per weight, 1 = kept: bit 15 -> bit 0 of byte 0, bit 31 -> bit 0 of byte 1 of each pair
+    const uint32_t b0 = (k0 >> 15) & 1u, b1 = (k0 >> 23) & 0x100u, b2 = (k1 >> 15) & 1u, b3 = (k1 >> 23) & 0x100u;
+    const uint32_t b4 = (k2 >> 15) & 1u, b5 = (k2 >> 23) & 0x100u, b6 = (k3 >> 15) & 1u, b7 = (k3 >> 23) & 0x100u;
+    mask[i] = make_uint2(b0 | b1 | ((b2 | b3) << 16), b4 | b5 | ((b6 | b7) << 16));
   }
   if (masked) {
-    // the reference multiplies by the 0/1 mask: a dropped weight becomes a signed zero, a kept NaN stays
-#pragma unroll
-    for (int t = 0; t < 8; ++t)
-      if (!((keep >> t) & 1u)) w[t] = ob_dropped_value(w[t]);
+    // the reference multiplies by the 0/1 mask: a dropped weight becomes a signed zero, a NaN stays a NaN
+    const uint32_t p0 = k0 | ob_nan2(v.x, 0x03ff03ffu), p1 = k1 | ob_nan2(v.y, 0x03ff03ffu);
+    const uint32_t p2 = k2 | ob_nan2(v.z, 0x03ff03ffu), p3 = k3 | ob_nan2(v.w, 0x03ff03ffu);
+    v.x &= ((p0 >> 15) * 0xffffu) | kObSign2;
+    v.y &= ((p1 >> 15) * 0xffffu) | kObSign2;
+    v.z &= ((p2 >> 15) * 0xffffu) | kObSign2;
+    v.w &= ((p3 >> 15) * 0xffffu) | kObSign2;
     masked[i] = v;
   }
 }

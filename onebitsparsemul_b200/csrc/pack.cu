@@ -23,6 +23,7 @@
 #include "formats.h"
 #include "kernels.h"
 #include "mask24.h"
+#include "pack16.h"
 
 namespace {
 
@@ -103,67 +104,89 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
     const int64_t row = mb * 128 + r, chunk = kb * 8 + c;
     const bool valid = row < a.m && chunk < nchunks;
 
-    T e[16];
+    unsigned meta = 0, even = 0, odd = 0;               // metadata word; signs of the first / second kept weight of each group
     if constexpr (kStaged) {
-      // rows and columns beyond the matrix were staged as zeros
-      *reinterpret_cast<uint4*>(&e[0]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16]);
-      *reinterpret_cast<uint4*>(&e[8]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16 + 8]);
-    } else if (valid) {
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.dense) + row * a.k + chunk * 16);
+      // 16-bit weights, two per register: mask, tests and encoder work on both halves and on all four groups at once
+      // (pack16.h). Rows and columns beyond the matrix were staged as zeros.
+      uint32_t x[8];
+      *reinterpret_cast<uint4*>(&x[0]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16]);
+      *reinterpret_cast<uint4*>(&x[4]) = *reinterpret_cast<const uint4*>(&s_dense[r * kRowStride + c * 16 + 8]);
+      if constexpr (DT == OB_DENSE_F16) {
+        if (a.apply_mask) {
 #pragma unroll
-      for (int v = 0; v < 16 / kElemsPer16B; ++v) {
-        const uint4 x = __ldg(src + v);
-        *reinterpret_cast<uint4*>(&e[v * kElemsPer16B]) = x;
+          for (int g = 0; g < 4; ++g) ob_mask_group2(x[2 * g], x[2 * g + 1]);
+          if (a.masked) {                                 // back into the staged tile; stored row-wise at the end
+            *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16]) = *reinterpret_cast<uint4*>(&x[0]);
+            *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16 + 8]) = *reinterpret_cast<uint4*>(&x[4]);
+          }
+        }
       }
-    } else {
+      uint32_t s0, s1;
+      meta = ob_encode_chunk16(x, DT == OB_DENSE_F16 ? 0x03ff03ffu : 0x007f007fu, s0, s1);
+      // reference bitfield: one ballot per kept value gives 32 rows of one bitfield column
+      if (a.bits_ref) {
 #pragma unroll
-      for (int t = 0; t < 16; ++t) e[t] = T(0);
-    }
-
-    if constexpr (DT == OB_DENSE_F16) {
-      if (a.apply_mask && valid) {
+        for (int t = 0; t < 8; ++t) {
+          const unsigned w = __ballot_sync(0xffffffffu, valid && ((((t & 1) ? s1 : s0) >> (4 * (t >> 1))) & 1u));
+          if (lane == 0) s_bits_ref[(c * 8 + t) * 4 + rg] = w;
+        }
+      }
+      if (!valid) continue;
+      even = ob_plane_to_nibble(s0);
+      odd = ob_plane_to_nibble(s1);
+      if (a.sparse) {                                     // the kept values themselves (exchange format, tests)
+        const T* e = reinterpret_cast<const T*>(x);
+        T kept[8];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const unsigned keep = ob_keep_mask4(&e[4 * g]);
-#pragma unroll
-          for (int t = 0; t < 4; ++t)
-            if (!((keep >> t) & 1u)) e[4 * g + t] = ob_dropped_value(e[4 * g + t]);
+          const int i0 = (meta >> (4 * g)) & 3, i1 = (meta >> (4 * g + 2)) & 3;
+          kept[2 * g] = i0 == 0 ? e[4 * g] : i0 == 1 ? e[4 * g + 1] : e[4 * g + 2];
+          kept[2 * g + 1] = i1 == 1 ? e[4 * g + 1] : i1 == 2 ? e[4 * g + 2] : e[4 * g + 3];
         }
-        if (a.masked) {                                 // back into the staged tile; stored row-wise at the end
-          *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16]) = *reinterpret_cast<uint4*>(&e[0]);
-          *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16 + 8]) = *reinterpret_cast<uint4*>(&e[8]);
-        }
+        *reinterpret_cast<uint4*>(static_cast<T*>(a.sparse) + row * (a.k / 2) + chunk * 8) = *reinterpret_cast<uint4*>(kept);
       }
-    }
-
-    unsigned meta = 0, signs = 0;
-    T kept[8];
+    } else {
+      T e[16];
+      if (valid) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.dense) + row * a.k + chunk * 16);
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const unsigned nib = ob_encode_group(Tr::nonzero(e[4 * g]), Tr::nonzero(e[4 * g + 1]),
-                                           Tr::nonzero(e[4 * g + 2]), Tr::nonzero(e[4 * g + 3]));
-      meta |= nib << (4 * g);
-      const int i0 = nib & 3, i1 = nib >> 2;
-      // a 4-way select keeps e[] in registers (no dynamic indexing)
-      const T v0 = i0 == 0 ? e[4 * g] : i0 == 1 ? e[4 * g + 1] : e[4 * g + 2];
-      const T v1 = i1 == 1 ? e[4 * g + 1] : i1 == 2 ? e[4 * g + 2] : e[4 * g + 3];
-      kept[2 * g] = v0; kept[2 * g + 1] = v1;
-      signs |= (Tr::positive(v0) ? 1u : 0u) << (2 * g);
-      signs |= (Tr::positive(v1) ? 1u : 0u) << (2 * g + 1);
-    }
-
-    // reference bitfield: one ballot per kept value gives 32 rows of one bitfield column
+        for (int v = 0; v < 16 / kElemsPer16B; ++v) {
+          const uint4 x = __ldg(src + v);
+          *reinterpret_cast<uint4*>(&e[v * kElemsPer16B]) = x;
+        }
+      } else {
 #pragma unroll
-    for (int t = 0; t < 8; ++t) {
-      const unsigned w = __ballot_sync(0xffffffffu, valid && ((signs >> t) & 1u));
-      if (lane == 0) s_bits_ref[(c * 8 + t) * 4 + rg] = w;
-    }
-    if (!valid) continue;
-
-    if (a.sparse) {
-      uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.sparse) + row * (a.k / 2) + chunk * 8);
+        for (int t = 0; t < 16; ++t) e[t] = T(0);
+      }
+      unsigned signs = 0;
+      T kept[8];
 #pragma unroll
-      for (int v = 0; v < 8 / kElemsPer16B; ++v) dst[v] = *reinterpret_cast<uint4*>(&kept[v * kElemsPer16B]);
+      for (int g = 0; g < 4; ++g) {
+        const unsigned nib = ob_encode_group(Tr::nonzero(e[4 * g]), Tr::nonzero(e[4 * g + 1]),
+                                             Tr::nonzero(e[4 * g + 2]), Tr::nonzero(e[4 * g + 3]));
+        meta |= nib << (4 * g);
+        const int i0 = nib & 3, i1 = nib >> 2;
+        // a 4-way select keeps e[] in registers (no dynamic indexing)
+        const T v0 = i0 == 0 ? e[4 * g] : i0 == 1 ? e[4 * g + 1] : e[4 * g + 2];
+        const T v1 = i1 == 1 ? e[4 * g + 1] : i1 == 2 ? e[4 * g + 2] : e[4 * g + 3];
+        kept[2 * g] = v0; kept[2 * g + 1] = v1;
+        signs |= (Tr::positive(v0) ? 1u : 0u) << (2 * g);
+        signs |= (Tr::positive(v1) ? 1u : 0u) << (2 * g + 1);
+      }
+      // reference bitfield: one ballot per kept value gives 32 rows of one bitfield column
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const unsigned w = __ballot_sync(0xffffffffu, valid && ((signs >> t) & 1u));
+        if (lane == 0) s_bits_ref[(c * 8 + t) * 4 + rg] = w;
+      }
+      if (!valid) continue;
+      if (a.sparse) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<T*>(a.sparse) + row * (a.k / 2) + chunk * 8);
+#pragma unroll
+        for (int v = 0; v < 8 / kElemsPer16B; ++v) dst[v] = *reinterpret_cast<uint4*>(&kept[v * kElemsPer16B]);
+      }
+      even = (signs & 1u) | ((signs >> 1) & 2u) | ((signs >> 2) & 4u) | ((signs >> 3) & 8u);
+      odd = ((signs >> 1) & 1u) | ((signs >> 2) & 2u) | ((signs >> 3) & 4u) | ((signs >> 4) & 8u);
     }
     // tile-ordered metadata
     {
@@ -171,13 +194,9 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
       s_meta_tile[(r0 + 8 * c1 + 16 * r2) * 8 + 2 * c2 + r1] = (uint16_t)meta;
     }
     // tile-ordered sign bits: even kept values to bits 4*(c&3).., odd ones 16 higher
-    {
-      const unsigned even = (signs & 1u) | ((signs >> 1) & 2u) | ((signs >> 2) & 4u) | ((signs >> 3) & 8u);
-      const unsigned odd = ((signs >> 1) & 1u) | ((signs >> 2) & 2u) | ((signs >> 3) & 4u) | ((signs >> 4) & 8u);
-      atomicOr(&s_bits_tile[r * 2 + (c >> 2)], (even << (4 * (c & 3))) | (odd << (16 + 4 * (c & 3))));
-    }
+    atomicOr(&s_bits_tile[r * 2 + (c >> 2)], (even << (4 * (c & 3))) | (odd << (16 + 4 * (c & 3))));
     // reference-ordered metadata: destination stays inside this tile's 4 chunk pairs x 128 rows
-    {
+    if (a.meta_ref) {
       unsigned rs, cs;                                                  // shuffled row and column inside the tile
       ob_meta_ref_position_local(a.dialect, (unsigned)r, (unsigned)c, &rs, &cs);
       s_meta_ref[(cs >> 1) * 256 + rs * 2 + (cs & 1)] = (uint16_t)meta;

@@ -22,6 +22,18 @@ namespace {
 // permuted there, and stored in tile order (3 KiB contiguous per tile).
 constexpr int kRB = 4;
 
+// 32 x 32 bit transpose across a warp: lane l holds row l; afterwards bit l of lane j's word is what bit j of lane
+// l's word was. Five butterfly stages of one shuffle each (a ballot per output word costs three times as much).
+__device__ __forceinline__ uint32_t transpose32(uint32_t x, int lane) {
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) {
+    const uint32_t m = s == 16 ? 0x0000ffffu : s == 8 ? 0x00ff00ffu : s == 4 ? 0x0f0f0f0fu : s == 2 ? 0x33333333u : 0x55555555u;
+    const uint32_t y = __shfl_xor_sync(0xffffffffu, x, s);
+    x = (lane & s) ? (((y >> s) & m) | (x & ~m)) : ((x & m) | ((y & m) << s));
+  }
+  return x;
+}
+
 __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restrict__ bits_ref,
                                                           const uint16_t* __restrict__ meta_ref, int dialect,
                                                           int64_t m, int64_t k, uint32_t* __restrict__ bits_tile,
@@ -50,34 +62,32 @@ __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restr
   __syncthreads();
 
   // sign bits: warp = (32-row group, half of the 64 kept values). Lane l takes the bitfield word of the kept
-  // value whose tile-order bit position is l; ballot j then is tile row j's word.
+  // value whose tile-order bit position is l; after the transpose lane j holds tile row j's word.
   {
     const int rg = warp & 3, half = warp >> 2;
     const int q_local = half * 32 + 2 * (lane & 15) + (lane >> 4);
-    for (int rb = 0; rb < nrb; ++rb) {
-      const uint32_t w = s_bits[(q_local * kRB + rb) * 4 + rg];
-      uint32_t mine = 0;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const uint32_t b = __ballot_sync(0xffffffffu, (w >> j) & 1u);
-        if (lane == j) mine = b;
-      }
-      s_out[rb * 256 + (rg * 32 + lane) * 2 + half] = mine;
-    }
+    for (int rb = 0; rb < nrb; ++rb)
+      s_out[rb * 256 + (rg * 32 + lane) * 2 + half] = transpose32(s_bits[(q_local * kRB + rb) * 4 + rg], lane);
   }
   // metadata: thread u < 128 of each half of the CTA assembles lane u of a tile block (8 words: chunk pairs
-  // c2 = 0..3, rows r and r + 8); the two halves work on two row blocks at a time
-  for (int rb = t >> 7; rb < nrb; rb += 2) {
+  // c2 = 0..3, rows r and r + 8); the two halves work on two row blocks at a time. Where a word comes from does
+  // not depend on the row block.
+  {
     const unsigned u = t & 127, r0 = u & 7, c1 = (u >> 3) & 1, r2 = u >> 4;
-    __align__(16) uint16_t out[8];
+    unsigned src[8];
 #pragma unroll
     for (unsigned wd = 0; wd < 8; ++wd) {
       const unsigned c2 = wd >> 1, r1 = wd & 1;
       unsigned rs, cs;
       ob_meta_ref_position_local(dialect, r0 + 8 * r1 + 16 * r2, 2 * c2 + c1, &rs, &cs);
-      out[wd] = s_meta[((cs >> 1) * kRB + rb) * 256 + rs * 2 + (cs & 1)];
+      src[wd] = (cs >> 1) * (kRB * 256) + rs * 2 + (cs & 1);
     }
-    reinterpret_cast<uint4*>(meta_tile)[((mb0 + rb) * (k / 128) + kb) * 128 + u] = *reinterpret_cast<const uint4*>(out);
+    for (int rb = t >> 7; rb < nrb; rb += 2) {
+      __align__(16) uint16_t out[8];
+#pragma unroll
+      for (int wd = 0; wd < 8; ++wd) out[wd] = s_meta[src[wd] + rb * 256];
+      reinterpret_cast<uint4*>(meta_tile)[((mb0 + rb) * (k / 128) + kb) * 128 + u] = *reinterpret_cast<const uint4*>(out);
+    }
   }
   __syncthreads();
   {
