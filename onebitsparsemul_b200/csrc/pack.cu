@@ -27,6 +27,41 @@
 
 namespace {
 
+// The per-weight tests of a chunk as half2 comparisons: one FMA-pipe instruction per register of two weights and
+// test, where the integer forms of pack16.h take three to four ALU-pipe instructions (the kernel is bound by the
+// ALU pipe). A comparison mask is 0xffff in the halves where it holds.
+//   non-zero = unordered-or-not-equal to 0 (a NaN is non-zero, -0 is not)
+//   positive = greater than 0 (false for a NaN, for +-0 and for negative values; true for +inf and subnormals)
+template <int DT> __device__ __forceinline__ void chunk_masks(const uint32_t (&x)[8], uint32_t& M, uint32_t& P) {
+  uint32_t m2 = 0, p2 = 0;                                 // bits 2i and 16 + 2i: weights 2i and 2i + 1
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t nz, pos;
+    if constexpr (DT == OB_DENSE_F16) {
+      const __half2 v = *reinterpret_cast<const __half2*>(&x[i]), z = __half2half2(__ushort_as_half(0));
+      nz = __hneu2_mask(v, z);
+      pos = __hgt2_mask(v, z);
+    } else {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&x[i]), z = __bfloat162bfloat162(__ushort_as_bfloat16(0));
+      nz = __hneu2_mask(v, z);
+      pos = __hgt2_mask(v, z);
+    }
+    m2 |= nz & (0x00010001u << (2 * i));
+    p2 |= pos & (0x00010001u << (2 * i));
+  }
+  M = (m2 | (m2 >> 15)) & 0xffffu;
+  P = (p2 | (p2 >> 15)) & 0xffffu;
+}
+
+// ob_mask_group2 of pack16.h with the NaN test as a half2 comparison (x != x)
+__device__ __forceinline__ void mask_group2_f16(uint32_t& w0, uint32_t& w1) {
+  uint32_t keep0, keep1;
+  ob_keep_group2(w0, w1, keep0, keep1);
+  const __half2 h0 = *reinterpret_cast<const __half2*>(&w0), h1 = *reinterpret_cast<const __half2*>(&w1);
+  w0 &= ((keep0 >> 15) * 0xffffu) | __hneu2_mask(h0, h0) | kObSign2;
+  w1 &= ((keep1 >> 15) * 0xffffu) | __hneu2_mask(h1, h1) | kObSign2;
+}
+
 template <int DT> struct DenseTraits;
 template <> struct DenseTraits<OB_DENSE_F16> {
   using T = uint16_t;
@@ -114,15 +149,16 @@ __global__ void __launch_bounds__(256) ob_pack_kernel(PackArgs a) {
       if constexpr (DT == OB_DENSE_F16) {
         if (a.apply_mask) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) ob_mask_group2(x[2 * g], x[2 * g + 1]);
+          for (int g = 0; g < 4; ++g) mask_group2_f16(x[2 * g], x[2 * g + 1]);
           if (a.masked) {                                 // back into the staged tile; stored row-wise at the end
             *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16]) = *reinterpret_cast<uint4*>(&x[0]);
             *reinterpret_cast<uint4*>(&s_dense[r * kRowStride + c * 16 + 8]) = *reinterpret_cast<uint4*>(&x[4]);
           }
         }
       }
-      uint32_t s0, s1;
-      meta = ob_encode_chunk16(x, DT == OB_DENSE_F16 ? 0x03ff03ffu : 0x007f007fu, s0, s1);
+      uint32_t M, P, s0, s1;
+      chunk_masks<DT>(x, M, P);
+      meta = ob_encode_planes(M, P, s0, s1);
       // reference bitfield: one ballot per kept value gives 32 rows of one bitfield column
       if (a.bits_ref) {
 #pragma unroll

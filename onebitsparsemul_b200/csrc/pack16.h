@@ -10,7 +10,9 @@
 //   * the metadata encoder of sparse_semi_structured_from_dense_cutlass (:54-179; its minimised boolean
 //     functions, :133-141) runs on bit planes that hold one bit per group, i.e. once per chunk.
 // Plain integer C++, so the same code is checked on the host against the element-wise statement of the rules
-// (tests of the oracle's rules live with the oracle; this header only has to agree with mask24.h and formats.h).
+// (tests/host/pack16_check.cpp; this header only has to agree with mask24.h and formats.h). The kernels replace the
+// per-weight tests by half2 comparisons (FMA pipe) where the data type has them; the integer forms here define
+// what those must return.
 #pragma once
 #include <stdint.h>
 
@@ -70,9 +72,24 @@ OB_HD void ob_mask_group2(uint32_t& w0, uint32_t& w1) {
   w1 &= ((pass1 >> 15) * 0xffffu) | kObSign2;
 }
 
-// Encodes one chunk. x[8]: the 16 weights (after the mask, if any). Returns the canonical metadata word
-// (nibble g = the two 2-bit positions of group g's kept weights); s0 / s1: bit 4g set = the first / second kept
-// weight of group g is positive (sign bit clear, not zero, not NaN).
+// The encoder on bit masks of a chunk: M / P bit j set = weight j is non-zero / positive (sign bit clear, not zero,
+// not NaN). Returns the canonical metadata word (nibble g = the two 2-bit positions of group g's kept weights);
+// s0 / s1: bit 4g set = the first / second kept weight of group g is positive.
+OB_HD uint32_t ob_encode_planes(uint32_t M, uint32_t P, uint32_t& s0, uint32_t& s1) {
+  constexpr uint32_t g = 0x1111u;                          // one bit per group
+  const uint32_t m0 = M & g, m1 = (M >> 1) & g, m3 = (M >> 3) & g;
+  const uint32_t b0 = m1 & ~m0, b1 = g & ~(m0 | m1);
+  const uint32_t b2 = (m0 & m1) | b1 | m3, b3 = b0 | (g & ~m1);
+  const uint32_t p0 = P & g, p1 = (P >> 1) & g, p2 = (P >> 2) & g, p3 = (P >> 3) & g;
+  // first kept position = (b1 b0) in {0, 1, 2}, second = (b3 b2) in {1, 2, 3}
+  const uint32_t lo01 = (b0 & p1) | (~b0 & p0);
+  s0 = ((b1 & p2) | (~b1 & lo01)) & g;
+  const uint32_t hi23 = (b2 & p3) | (~b2 & p2);
+  s1 = ((b3 & hi23) | (~b3 & p1)) & g;
+  return b0 | (b1 << 1) | (b2 << 2) | (b3 << 3);
+}
+
+// Encodes one chunk with integer arithmetic only. x[8]: the 16 weights (after the mask, if any).
 OB_HD uint32_t ob_encode_chunk16(const uint32_t x[8], uint32_t nan_add2, uint32_t& s0, uint32_t& s1) {
   uint32_t nzg = 0, posg = 0;                              // bits 2i and 16 + 2i: weight 2i, 2i + 1 of the chunk
 #pragma unroll
@@ -82,19 +99,7 @@ OB_HD uint32_t ob_encode_chunk16(const uint32_t x[8], uint32_t nan_add2, uint32_
     nzg |= nz >> (15 - 2 * i);
     posg |= pos >> (15 - 2 * i);
   }
-  const uint32_t M = (nzg | (nzg >> 15)) & 0xffffu, P = (posg | (posg >> 15)) & 0xffffu;   // bit j = weight j
-  constexpr uint32_t g = 0x1111u;                          // one bit per group
-  const uint32_t m0 = M & g, m1 = (M >> 1) & g, m3 = (M >> 3) & g;
-  const uint32_t b0 = m1 & ~m0, b1 = g & ~(m0 | m1);
-  const uint32_t b2 = (m0 & m1) | b1 | m3, b3 = b0 | (g & ~m1);
-  const uint32_t p0 = P & g, p1 = (P >> 1) & g, p2 = (P >> 2) & g, p3 = (P >> 3) & g;
-  // first kept position = (b1 b0) in {0, 1, 2}, second = (b3 b2) in {1, 2, 3}
-  const uint32_t lo01 = (b0 & p1) | (~b0 & p0);
-  s0 = (b1 & p2) | (~b1 & lo01);
-  const uint32_t hi23 = (b2 & p3) | (~b2 & p2);
-  s1 = ((b3 & hi23) | (~b3 & p1)) & g;
-  s0 &= g;
-  return b0 | (b1 << 1) | (b2 << 2) | (b3 << 3);
+  return ob_encode_planes((nzg | (nzg >> 15)) & 0xffffu, (posg | (posg >> 15)) & 0xffffu, s0, s1);
 }
 
 // bits 0, 4, 8, 12 of a plane -> bits 0, 1, 2, 3

@@ -56,10 +56,10 @@ def test_pack_matches_reference_golden(lib, golden, case, code):
 def test_pack_matches_oracle(lib, m, k, dialect):
     rng = np.random.default_rng(m * 7 + k)
     dense, _ = helpers.make_weights(rng, m, k)
-    # sprinkle encoder corner cases: extra non-zeros, missing non-zeros, -0.0, NaN
+    # sprinkle encoder corner cases: extra non-zeros, missing non-zeros, -0.0, NaN, infinities, subnormals
     flat = dense.reshape(-1)
     idx = rng.integers(0, flat.size, size=max(8, flat.size // 50))
-    flat[idx] = rng.choice(np.array([0.0, -0.0, 3.0, -2.0, np.nan], np.float16), size=idx.size)
+    flat[idx] = rng.choice(np.array([0.0, -0.0, 3.0, -2.0, np.nan, np.inf, -np.inf, 6e-8, -6e-8, 3e-5, -3e-5], np.float16), size=idx.size)
     tiled = m % 128 == 0 and k % 128 == 0
     a_bits, e_meta, sparse, bits_tile, meta_tile = gpu_pack(lib, dense, _lib.DENSE_F16, dialect, tiled=tiled)
     canon, signs, osparse = oracle.compress(dense)
@@ -124,6 +124,8 @@ def test_fused_mask_and_pack_equals_the_two_passes(lib, golden, m, k):
     dense[rng.random((m, k)) < 0.1] = np.float16(1.0)                      # ties
     dense[rng.random((m, k)) < 0.01] = np.float16(np.nan)
     dense[rng.random((m, k)) < 0.01] = np.float16(np.inf)
+    dense[rng.random((m, k)) < 0.01] = np.float16(-6e-8)       # subnormals
+    dense[rng.random((m, k)) < 0.01] = np.float16(6e-8)
     d = dev(dense)
     tiled = m % 128 == 0 and k % 128 == 0
 
