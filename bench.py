@@ -181,7 +181,13 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = max(64, min(512, int(512 * (8192.0 / args.size) ** 2) // 64 * 64))     # about the same work per step at every size; whole 64-row groups (metadata shuffle)
+    # Rows per step: whole 64-row groups (metadata shuffle), as many as keep the whole run near 2.5 minutes, at most the
+    # ~1e12 flop of the cpu_baseline leg. A call of the oracle costs a fixed ~1.7 s at 25600 (it converts the tokens)
+    # plus ~8.4 ms per row; small samples would time the conversion, not the GEMM.
+    per_step_s = 150.0 / max(1, args.warmup + args.steps)
+    scale = (args.size / 25600.0) ** 2
+    rows = int(max(0.0, per_step_s - 1.7 * scale) / (0.0084 * scale)) // 64 * 64
+    rows = max(64, min(rows, args.size, max(64, int(1e12 / (2.0 * args.size * args.size)) // 64 * 64)))
     cpu = CpuSample(args.size, rows)
     vals = []
     for i in range(args.warmup + args.steps):
