@@ -20,7 +20,7 @@ namespace {
 // shuffles of both dialects stay inside a 128-row block). With kRB = 4 a segment is two whole 32-byte sectors and a
 // CTA has 12 KiB of loads in flight; everything is requested before anything is used, staged in shared memory,
 // permuted there, and stored in tile order (3 KiB contiguous per tile).
-constexpr int kRB = 4;
+constexpr int kRB = 4;                                    // measured: 2 and 8 are slower at every size
 
 // 32 x 32 bit transpose across a warp: lane l holds row l; afterwards bit l of lane j's word is what bit j of lane
 // l's word was. Five butterfly stages of one shuffle each (a ballot per output word costs three times as much).
@@ -46,18 +46,27 @@ __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restr
   const int nrb = (int)min((int64_t)kRB, m / 128 - mb0);   // row blocks of this column that exist
 
   {
-    const int q = t / kRB, rb = t % kRB;                   // 64 segments x kRB pieces of 16 bytes
-    uint4 vb = make_uint4(0, 0, 0, 0), vm[2];
-    if (rb < nrb) vb = __ldg(reinterpret_cast<const uint4*>(bits_ref + ((kb * 64 + q) * m + (mb0 + rb) * 128) / 8));
+    constexpr int kBitPieces = 64 * kRB, kMetaPieces = 4 * kRB * 32;           // 16-byte pieces of the column
+    constexpr int kBitLoads = (kBitPieces + 255) / 256, kMetaLoads = (kMetaPieces + 255) / 256;
+    uint4 vb[kBitLoads], vm[kMetaLoads];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kBitLoads; ++i) {
+      const int idx = t + 256 * i, q = idx / kRB, rb = idx % kRB;                 // 64 segments x kRB pieces
+      vb[i] = make_uint4(0, 0, 0, 0);
+      if (idx < kBitPieces && rb < nrb) vb[i] = __ldg(reinterpret_cast<const uint4*>(bits_ref + ((kb * 64 + q) * m + (mb0 + rb) * 128) / 8));
+    }
+#pragma unroll
+    for (int i = 0; i < kMetaLoads; ++i) {
       const int idx = t + 256 * i, pair = idx / (kRB * 32), rem = idx % (kRB * 32);   // 4 runs x kRB * 32 pieces
       vm[i] = make_uint4(0, 0, 0, 0);
-      if (rem / 32 < nrb) vm[i] = __ldg(reinterpret_cast<const uint4*>(meta_ref + (kb * 4 + pair) * 2 * m + mb0 * 256 + rem * 8));
+      if (idx < kMetaPieces && rem / 32 < nrb) vm[i] = __ldg(reinterpret_cast<const uint4*>(meta_ref + (kb * 4 + pair) * 2 * m + mb0 * 256 + rem * 8));
     }
-    reinterpret_cast<uint4*>(s_bits)[t] = vb;
-    reinterpret_cast<uint4*>(s_meta)[t] = vm[0];
-    reinterpret_cast<uint4*>(s_meta)[t + 256] = vm[1];
+#pragma unroll
+    for (int i = 0; i < kBitLoads; ++i)
+      if (t + 256 * i < kBitPieces) reinterpret_cast<uint4*>(s_bits)[t + 256 * i] = vb[i];
+#pragma unroll
+    for (int i = 0; i < kMetaLoads; ++i)
+      if (t + 256 * i < kMetaPieces) reinterpret_cast<uint4*>(s_meta)[t + 256 * i] = vm[i];
   }
   __syncthreads();
 
@@ -90,9 +99,9 @@ __global__ void __launch_bounds__(256) ob_relayout_kernel(const uint8_t* __restr
     }
   }
   __syncthreads();
-  {
-    const int rb = t >> 6, i = t & 63;
-    if (rb < nrb) reinterpret_cast<uint4*>(bits_tile)[((mb0 + rb) * (k / 128) + kb) * 64 + i] = reinterpret_cast<const uint4*>(s_out)[t];
+  for (int idx = t; idx < 64 * kRB; idx += 256) {
+    const int rb = idx >> 6, i = idx & 63;
+    if (rb < nrb) reinterpret_cast<uint4*>(bits_tile)[((mb0 + rb) * (k / 128) + kb) * 64 + i] = reinterpret_cast<const uint4*>(s_out)[idx];
   }
 }
 
