@@ -7,7 +7,6 @@
 #include <stdint.h>
 
 #include "kernels.h"
-#include "mask24.h"
 #include "pack16.h"
 
 namespace {

@@ -1,5 +1,6 @@
-// The 2:4 magnitude mask of one group of four fp16 weights, shared by the stand-alone mask kernel (mask.cu) and
-// the pack kernel's fused form (pack.cu). Restates mask_creator of the reference
+// The 2:4 magnitude mask of one group of four fp16 weights, stated weight by weight. The kernels (mask.cu, pack.cu)
+// compute the same thing two weights per register (pack16.h); tests/host/pack16_check.cpp checks that form against
+// this one. Restates mask_creator of the reference
 // (onebit_sparse_mul/_semi_structured_conversions.py:286-314: abs, argsort per group of 4, zero the two
 // smallest); torch.argsort leaves the order of equal magnitudes unspecified, here the lower index is dropped first.
 #pragma once

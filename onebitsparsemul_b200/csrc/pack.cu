@@ -22,7 +22,6 @@
 
 #include "formats.h"
 #include "kernels.h"
-#include "mask24.h"
 #include "pack16.h"
 
 namespace {
