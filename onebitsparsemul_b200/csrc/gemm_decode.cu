@@ -4,7 +4,7 @@
 // Replaces the reference's 128x64x128 CUTLASS threadblock (csrc/kernel.h:23-25) for the shapes
 // where its 64-wide token tile is almost empty. Such a call moves only a few MiB, so the kernel is
 // built to be short: the whole grid is one wave, every weight byte of a CTA is requested in the
-// first few hundred cycles, and there is at most one cluster-wide synchronisation in its life.
+// first few hundred cycles, and no cluster-wide barrier stands between its last MMA and its result.
 //   * one CTA = one 128-row block of A x one slice of K (a cluster of S CTAs cuts K into S slices);
 //   * weights: the tile order keeps the metadata (2 KiB) and sign (1 KiB) blocks of consecutive
 //     k tiles of a row block adjacent, so a round of KL tiles is two bulk async copies into a
@@ -23,14 +23,14 @@
 //     fragment register is one 32-bit load; the global loads of all rounds in the ring are issued together;
 //   * reduction: the KL partial sums of a CTA are added through shared memory (the drained weight
 //     ring); with S > 1 every thread then PUSHES 16 bytes of sums through distributed shared memory into
-//     the CTA that owns those output rows (remote stores are slow to issue: one per thread), and after
-//     the single cluster barrier each CTA adds the S slices in a fixed order, scales, converts and
-//     stores. No atomics, no scratch in HBM, no remote reads, deterministic;
+//     the CTA that owns those output rows (remote stores are slow to issue: one per thread). The store is an
+//     st.async that completes on the owner's mbarrier, so data and signal travel together; each CTA waits for its
+//     own barrier only, then adds the S slices in a fixed order, scales, converts and stores. No atomics, no
+//     scratch in HBM, no remote reads, no cluster barrier after start-up, deterministic;
 //   * programmatic dependent launch: the grid may start while the previous kernel of the stream
 //     drains. Packed weights are long-lived, so their loads go out first; the tokens are read, and
 //     global memory is written, only after griddepcontrol.wait.
 // Every mbarrier wait is bounded; a wait that gives up records a code in g_decode_status.
-#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -41,7 +41,6 @@
 #include "kernels.h"
 #include "sm100_ptx.h"
 
-namespace cg = cooperative_groups;
 
 namespace {
 
@@ -80,8 +79,9 @@ template <int NT> struct DecodeCfg {
   static constexpr int kRecv = 128 * NP * 4;                                  // [source rank][row of this CTA's share][token]
   static constexpr int kRed = KL * 128 * NP * 4;                              // [tile lane][row][token], reuses the drained ring
   static_assert(kRed <= kWeights + kTokens, "the reduction buffer must fit the drained ring");
-  static constexpr int kBars = 2 * kRing * 8;                                 // [full | empty][slot]
+  static constexpr int kBars = (2 * kRing + 2) * 8;                           // [full | empty][slot], the receive barrier, 8 bytes of padding: what follows is accessed 16 bytes at a time
   static constexpr int kZeroRow = (kTokStride * 2 + 15) / 16 * 16;            // a token row of zeros
+  static_assert(kBars % 16 == 0 && kRecv % 16 == 0 && (kWeights + kTokens) % 16 == 0, "the zero row behind the barriers is written with 16-byte stores");
   static constexpr int kTotal = kWeights + kTokens + kRecv + kBars + kZeroRow;
   static_assert(2 * (kTotal + 1024) <= 227 * 1024, "two CTAs per SM must fit");
   static_assert(KL * OB_TILE_K * NP / 8 == kPieces * kThreads, "a round's tokens are whole 16-byte pieces per thread");
@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
   if (tid < L::kZeroRow / 16) reinterpret_cast<uint4*>(smem + L::kWeights + L::kTokens + L::kRecv + L::kBars)[tid] = make_uint4(0, 0, 0, 0);
   auto bar_full = [&](int s) { return bar0 + 8 * s; };
   auto bar_empty = [&](int s) { return bar0 + 8 * (kRing + s); };
+  const uint32_t bar_recv = bar0 + 8 * (2 * kRing);           // every slice's sums for this CTA's rows have landed
 
   const int tiles_k = (int)(a.k / OB_TILE_K);
   const int tile_begin = (int)((int64_t)tiles_k * rank / S), tile_end = (int)((int64_t)tiles_k * (rank + 1) / S);
@@ -154,7 +155,9 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
   if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid == 0) {
     for (int s = 0; s < kRing; ++s) { ob_ptx::mbar_init(bar_full(s), 1); ob_ptx::mbar_init(bar_empty(s), kThreads / 32); }
+    ob_ptx::mbar_init(bar_recv, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (S > 1) ob_ptx::mbar_expect_tx(bar_recv, (uint32_t)L::kRecv);          // S slices x 128 / S rows x NP sums
     const int npre = min(nrounds, kRing);
     for (int r = 0; r < npre; ++r) issue(r);
   }
@@ -349,7 +352,6 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
   // each thread adds the lanes for NT groups of four consecutive tokens of one row
   constexpr int kQuads = 128 * NP / 4;                        // = NT * kThreads
   const int rows_per = 128 / S;                               // S is a power of two
-  cg::cluster_group cluster = cg::this_cluster();
   if (S > 1) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // all CTAs of the cluster have started
 #pragma unroll
   for (int i = 0; i < kQuads / kThreads; ++i) {
@@ -369,13 +371,17 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
       finish(grow, j + 2, v.z, scale, bias); finish(grow, j + 3, v.w, scale, bias);
     } else {
       // 5. one 16-byte push to the CTA that owns the row: CTA q of the cluster owns rows [q * 128/S, (q+1) * 128/S)
-      float* dst = cluster.map_shared_rank(s_recv, row / rows_per) + ((rank * rows_per + row % rows_per) * NP + j);
-      *reinterpret_cast<float4*>(dst) = v;
+      //    The store completes on the owner's mbarrier: data and signal travel together, no cluster-wide barrier
+      //    stands between the last MMA and the sum.
+      const uint32_t owner = (uint32_t)(row / rows_per);
+      const uint32_t local = ob_ptx::smem_u32(s_recv) + (uint32_t)(((rank * rows_per + row % rows_per) * NP + j) * 4);
+      asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                   ::"r"(ob_ptx::map_to_cta(local, owner)), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "r"(ob_ptx::map_to_cta(bar_recv, owner)) : "memory");
     }
   }
   if (S == 1) { OB_TRACE_EV(7); return; }
   OB_TRACE_EV(5);
-  // the per-row constants of this thread's outputs, fetched while the barrier is pending
+  // the per-row constants of this thread's outputs, fetched while the sums travel
   constexpr int kOut = (128 * NP / 2 + kThreads - 1) / kThreads;   // outputs per thread at S = 2, the most
   float sc[kOut], bs[kOut];
 #pragma unroll
@@ -389,7 +395,7 @@ __global__ void __launch_bounds__(DecodeCfg<NT>::kThreads, 2) ob_gemm_decode_ker
       if (a.bias) bs[i] = __half2float(a.bias[row]);
     }
   }
-  cluster.sync();                                             // the only cluster-wide barrier
+  ob_ptx::mbar_wait(bar_recv, 0, budget, &g_decode_status, 103);   // all S slices of this CTA's rows are here
   OB_TRACE_EV(6);
 
   // 6. fixed-order sum of the S slices from this CTA's own shared memory
