@@ -489,14 +489,14 @@ def run_ours(args):
     Ch = torch.empty((rows, S), dtype=torch.float16).pin_memory()
 
     def e2e_step():
-        ob.matmul_packed_host(pw, Bh, Ch)
+        layer.forward_host(Bh, Ch)                 # one rank: onebit_matmul_packed_host; several: 1/world of B per rank + NVLink all-gather
 
     for _ in range(2):
         e2e_step()
     e2e_steps = max(2, min(args.steps, 5))
     e2e_ms = timed(e2e_step, e2e_steps, sync_all, reduce_max)
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
-    h2d = reduce_max(float(Bh.numel() * 2)) * world
+    h2d = float(Bh.numel() * 2) if (world == 1 or S % world == 0) else float(Bh.numel() * 2) * world   # B crosses PCIe once per node
     d2h_t = torch.tensor([float(Ch.numel() * 2)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(d2h_t)
@@ -575,9 +575,11 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (B and C are 2*S*S bytes)", "pack_ms_rank0": pack_ms},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "ms_per_step": e2e_ms,
-                    "note": "onebit_matmul_packed_host on every rank: all tokens from pinned host memory, the rank's slab of "
-                            "the result to pinned host memory, copies overlapped with the GEMM in column panels; weights "
-                            "resident; bytes are summed over the ranks"},
+                    "note": "ShardedBinaryLinear.forward_host: tokens from pinned host memory, the rank's slab of the result to "
+                            "pinned host memory, weights resident. One rank: onebit_matmul_packed_host (copies overlapped with "
+                            "the GEMM in column panels). Several ranks: per column panel each rank uploads 1/N of the tokens, an NCCL "
+                            "all-gather over NVLink completes the panel, and the panel of the result leaves while the next "
+                            "panels travel and multiply. Bytes are summed over the ranks"},
             "gpu_launches": args.steps * world,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": sparse_peak, "unit": "TFLOP/s",
                          "frac": achieved / sparse_peak, "traffic": MEASURED_TRAFFIC.get(S) if world == 1 else None,

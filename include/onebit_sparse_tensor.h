@@ -140,6 +140,14 @@ int onebit_matmul_packed_host(const void *bits_tile, const void *meta_tile, cons
                               void *d_host, int64_t m, int64_t n, int64_t k, int out_type, void *workspace,
                               size_t workspace_bytes, void *stream);
 
+/* Pitched asynchronous copy between host and device (either direction, decided by the pointers): `rows` rows of
+ * `row_bytes` bytes, `dst_pitch` / `src_pitch` bytes from one row to the next. The building block of the
+ * host-buffer paths -- a column panel of a row-major matrix is such a block -- exported for callers that
+ * pipeline panels themselves (the row-sharded host path of onebitsparsemul_b200/sharded.py). Host memory must be
+ * page-locked for the copy to be asynchronous. No counterpart in the reference. */
+int onebit_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t row_bytes,
+                         size_t rows, void *stream);
+
 /* Dense (m, k) row-major weights -> packed operands in one pass; bit-exact replacement of
  * sparse_semi_structured_from_dense_cutlass + binary_quant + .T + pack_binary
  * (_semi_structured_conversions.py:54-179, onebit_sparse_mul/__init__.py:22-34,139-143).

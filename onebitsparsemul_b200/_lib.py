@@ -30,6 +30,7 @@ SIGNATURES = {
     "onebit_matmul_packed": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "onebit_linear_tokens": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "onebit_host_workspace_bytes": (_sz, [_i64, _i64, _i64, _int]),
+    "onebit_copy_2d_async": (_int, [_vp, _sz, _vp, _sz, _sz, _sz, _vp]),
     "onebit_matmul_packed_scatter": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _int, _i64, _i64, _i64, _vp]),
     "onebit_matmul_packed_host": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
     "onebit_pack_from_dense": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp, _vp]),

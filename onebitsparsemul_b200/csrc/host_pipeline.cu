@@ -147,3 +147,14 @@ extern "C" int onebit_matmul_packed_host(const void* bits_tile, const void* meta
   join();
   return ONEBIT_OK;
 }
+
+// Pitched copy between host and device, direction from the pointers; see the header.
+extern "C" int onebit_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                                    size_t rows, void* stream) {
+  if (!dst || !src) return fail(ONEBIT_ERR_NULL, "null pointer");
+  if (row_bytes == 0 || rows == 0) return ONEBIT_OK;
+  if (dst_pitch < row_bytes || src_pitch < row_bytes) return fail(ONEBIT_ERR_ARG, "a pitch is smaller than a row");
+  cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDefault, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy2DAsync");
+  return ONEBIT_OK;
+}

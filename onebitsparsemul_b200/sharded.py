@@ -18,6 +18,10 @@ only when the caller asks for the full C on every rank:
                     The returned tensor is that cached buffer: the next fused call of the same shape
                     overwrites it.
 
+``forward_host`` is the same GEMM for tokens and result in pinned host memory: in column panels, every rank uploads
+1/world of a panel, the shares are all-gathered over NVLink, and the panel of C goes back to the host while the next
+panels travel and multiply.
+
 One process per GPU, ``torch.distributed`` for the plumbing. Slabs are whole 256-row blocks so that
 every rank runs the same kernel variants as a single GPU would; results are bit-identical to the
 single-GPU run because no reduction crosses a slab boundary.
@@ -70,6 +74,7 @@ class ShardedBinaryLinear:
         self._scatter = scatter
         self._peer_buffer = peer_buffer  # (layer, n, device) -> what _peer_mapped_buffer returns; for CPU ranks
         self._fused = {}                 # n -> (full C, peers' base addresses, keep-alive objects)
+        self._host_state = {}            # n -> device copies of B and of this rank's C, and the copy stream (forward_host)
         self._flag = None
         self.fused_backend = None        # "symmetric_memory" or "ipc", once a fused buffer exists
 
@@ -142,6 +147,90 @@ class ShardedBinaryLinear:
         for w in dist.batch_isend_irecv(ops):
             w.wait()
         return full
+
+    # -- tokens and result in host memory -----------------------------------------------------------------
+    def forward_host(self, B_host, out_host=None, out_dtype=torch.float16, panels: int = 8):
+        """C_slab = W_slab @ B for tokens B (k, n) in pinned HOST memory -- the same B on every rank -- with this
+        rank's (rows_g, n) slab of the result written to pinned host memory.
+
+        One rank: the library's host-buffer pipeline (``onebit_matmul_packed_host``). Several ranks: B crosses
+        PCIe once per NODE, not once per rank. The tokens are cut into column panels (whole 256-token blocks); for
+        every panel each rank uploads only its 1/world share of the panel's rows (a pitched copy), one NCCL
+        all-gather over NVLink completes the panel in place, the slab GEMM runs on it, and the panel of the result
+        goes back to the host. Three slots rotate on three streams, so panel p + 1 travels in while panel p is
+        multiplied and panel p - 1 travels out: PCIe carries both directions at once and a call costs about
+        max(H2D, D2H) / world. Needs k % world == 0 and n % 8 == 0 (otherwise every rank uploads all of B, unpipelined).
+        The work is queued on the current stream; synchronise it before reading the result."""
+        from . import _lib, matmul_packed_host
+        n = B_host.shape[1]
+        if out_host is None:
+            out_host = torch.empty((self.rows, n), dtype=out_dtype).pin_memory()
+        if self.world == 1:
+            return matmul_packed_host(self.packed, B_host, out_host, out_dtype)
+        if B_host.is_cuda or not B_host.is_pinned() or B_host.dtype != torch.float16 or tuple(B_host.shape) != (self.k, n) \
+                or not B_host.is_contiguous():
+            raise ValueError("B_host must be a contiguous pinned CPU float16 tensor of shape (k, n)")
+        if out_host.is_cuda or not out_host.is_pinned() or tuple(out_host.shape) != (self.rows, n) or not out_host.is_contiguous():
+            raise ValueError("out_host must be a contiguous pinned CPU tensor of shape (rows of this rank, n)")
+        dev = self.packed.bits_tile.device
+        main = torch.cuda.current_stream(dev)
+        esz = out_host.element_size()
+        if self.k % self.world != 0 or n % 8 != 0:
+            # every rank uploads all of B; no pipeline
+            Bd = B_host.to(dev, non_blocking=True)
+            Cd = torch.empty((self.rows, n), dtype=out_host.dtype, device=dev)
+            self._gemm(Bd, Cd)
+            out_host.copy_(Cd, non_blocking=True)
+            return out_host
+        lib = _lib.load()
+        blocks = (n + ROW_BLOCK - 1) // ROW_BLOCK
+        width = ((blocks + panels - 1) // max(1, panels)) * ROW_BLOCK          # tokens per panel: whole 256-token blocks
+        slots = 3
+        st = self._host_state.get((n, out_host.dtype))
+        if st is None:
+            st = self._host_state[(n, out_host.dtype)] = dict(
+                B=[torch.empty(self.k * width, dtype=torch.float16, device=dev) for _ in range(slots)],
+                C=[torch.empty(self.rows * width, dtype=out_host.dtype, device=dev) for _ in range(slots)],
+                up=torch.cuda.Stream(device=dev), down=torch.cuda.Stream(device=dev))
+        up, down = st["up"], st["down"]
+        up.wait_stream(main)                                    # earlier work of the caller (and of the previous call) first
+        down.wait_stream(main)
+        share = self.k // self.world
+        r0 = self.rank * share
+        multiplied, drained = [None] * slots, [None] * slots
+        c0 = 0
+        p = 0
+        while c0 < n:
+            w = min(width, n - c0)
+            s = p % slots
+            Bp = st["B"][s][:self.k * w].view(self.k, w)
+            Cp = st["C"][s][:self.rows * w].view(self.rows, w)
+            mine = Bp[r0:r0 + share]
+            with torch.cuda.stream(up):
+                if multiplied[s] is not None:
+                    up.wait_event(multiplied[s])                # the GEMM that read this slot's tokens is done
+                _lib.check(lib.onebit_copy_2d_async(mine.data_ptr(), w * 2, B_host.data_ptr() + (r0 * n + c0) * 2, n * 2,
+                                                    w * 2, share, up.cuda_stream))
+                loaded = torch.cuda.Event()
+                loaded.record(up)
+            main.wait_event(loaded)
+            dist.all_gather_into_tensor(Bp, mine, group=self.group)     # in place: the share already sits at its offset
+            if drained[s] is not None:
+                main.wait_event(drained[s])                     # this slot's previous result has left
+            self._gemm(Bp, Cp)
+            multiplied[s] = torch.cuda.Event()
+            multiplied[s].record(main)
+            with torch.cuda.stream(down):
+                down.wait_event(multiplied[s])
+                _lib.check(lib.onebit_copy_2d_async(out_host.data_ptr() + c0 * esz, n * esz, Cp.data_ptr(), w * esz,
+                                                    w * esz, self.rows, down.cuda_stream))
+                drained[s] = torch.cuda.Event()
+                drained[s].record(down)
+            c0 += w
+            p += 1
+        main.wait_stream(down)
+        main.wait_stream(up)
+        return out_host
 
     # -- fused GEMM + all-gather ------------------------------------------------------------------------
     def _peer_mapped_buffer(self, n, dev):

@@ -156,6 +156,13 @@ def _gpu_worker(rank, world, port, q):
             for mode in ("all", "fused", "fused"):   # twice: the cached peer-mapped buffer is reused
                 if not bool((layer.forward(B, gather=mode) == want).all()):
                     ok.append((n, mode))
+            # tokens and result in pinned host memory: 1/world of B uploaded per rank, all-gathered, C slab back
+            Bh = B.cpu().pin_memory()
+            for _ in range(2):                       # twice: the cached device buffers and the copy stream are reused
+                Ch = layer.forward_host(Bh)
+                torch.cuda.synchronize()
+                if not bool((Ch == want[layer.start:layer.start + layer.rows].cpu()).all()):
+                    ok.append((n, "host"))
         ok = (ok == [], ok, layer.fused_backend)
         torch.cuda.synchronize()
         q.put((rank, ok))
@@ -177,6 +184,9 @@ def test_sharded_gemm_on_visible_gpus_matches_single_gpu():
         want = ob.matmul_packed(ob.pack_weight(w), B, out_dtype=torch.float16)
         for mode in ("none", "all", "fused"):
             assert (layer.forward(B, gather=mode) == want).all()
+        Ch = layer.forward_host(B.cpu().pin_memory())
+        torch.cuda.synchronize()
+        assert (Ch == want.cpu()).all()
         return
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
