@@ -421,12 +421,10 @@ cudaError_t launch2(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const Pr
 // tmap_c: tensor map of an fp16 output with the 128-byte swizzle -- C (m x n): boxes of 64 tokens x 128 rows;
 //         y (n x m): boxes of 64 features x 256 tokens -- or NULL (fp32 output, or an output that is not
 //         16-byte aligned): direct stores from registers
-cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, bool token_major,
-                                 const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
-                                 void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
-                                 cudaStream_t stream) {
-  // token blocks per rasterisation group: their panels (k x 256 fp16 each) should fill about a quarter of L2
-  // (measured at 25600^3: 14.19 ms with 1, 13.66 with 2, 13.72 with 4, 13.96 with 6, 14.13 with 8 blocks per group)
+// Token blocks (256 tokens) per rasterisation group of the CTA-pair kernels: the group's token panels (k x 256 fp16
+// each) should fill about a quarter of L2, so that they stay hot while one sweep over the row pairs streams the
+// weights past (measured at 25600^3: 14.19 ms with 1, 13.66 with 2, 13.72 with 4, 13.96 with 6, 14.13 with 8 blocks).
+int prefill_raster_group(int64_t m, int64_t k) {
   static int l2_bytes[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -437,6 +435,14 @@ cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tma
   // small weights stay in L2 whatever the order: keep the plain order, whose concurrent clusters share one panel
   if (m * k * 3 / 16 <= l2 / 4) group = 1;
   if (forced_group > 0) group = forced_group;
+  return group;
+}
+
+cudaError_t launch_gemm_prefill2(const CUtensorMap* tmap, const CUtensorMap* tmap_c, int ks, bool token_major,
+                                 const void* bits_tile, const void* meta_tile, const void* scale, const void* bias,
+                                 void* d, int64_t m, int64_t n, int64_t k, int out_type, int* status,
+                                 cudaStream_t stream) {
+  const int group = prefill_raster_group(m, k);
   Prefill2Args a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                  static_cast<const __half*>(scale), static_cast<const __half*>(bias), d, m, n, k, out_type, status,
                  tmap_c != nullptr, group};
