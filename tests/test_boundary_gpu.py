@@ -193,3 +193,22 @@ def test_llama_shaped_stack_replace_and_graph_decode_loop():
         _lib.check(_lib.load().onebit_check_device_status())
     m = measure_decode(stack, hidden, tokens=1, steps=5)
     assert m["linear_layers"] == 14 and m["us_per_step"] > 0
+
+
+def test_pitched_copy_helper_moves_a_column_panel_both_ways():
+    """onebit_copy_2d_async: a column panel of a row-major host matrix to a contiguous device buffer and back into
+    another host matrix (the building block of the row-sharded host path)."""
+    lib = _lib.load()
+    rows, cols, c0, w = 300, 1000, 128, 256
+    src = (torch.arange(rows * cols, dtype=torch.int32) % 2048 + 1).to(torch.float16).reshape(rows, cols).pin_memory()
+    dst = torch.zeros((rows, cols), dtype=torch.float16).pin_memory()
+    panel = torch.empty((rows, w), dtype=torch.float16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.onebit_copy_2d_async(panel.data_ptr(), w * 2, src.data_ptr() + c0 * 2, cols * 2, w * 2, rows, stream))
+    _lib.check(lib.onebit_copy_2d_async(dst.data_ptr() + c0 * 2, cols * 2, panel.data_ptr(), w * 2, w * 2, rows, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(panel.cpu(), src[:, c0:c0 + w])
+    assert torch.equal(dst[:, c0:c0 + w], src[:, c0:c0 + w])
+    assert not dst[:, :c0].any() and not dst[:, c0 + w:].any()
+    # a pitch smaller than a row is refused, nothing is copied
+    assert lib.onebit_copy_2d_async(panel.data_ptr(), w, src.data_ptr(), cols * 2, w * 2, rows, stream) == 5    # ONEBIT_ERR_ARG
