@@ -276,7 +276,7 @@ def decode_extras(ob, _lib, dev):
                         "gbs": round(alg / us / 1e3, 1), "frac_of_measured_hbm": round(alg / us / 1e3 / peaks["hbm_gbs"], 4),
                         "weight_pool_mb": round(copies * weight_bytes / 1e6, 1)})
         del pool
-    return {"kernel": "ob_gemm_fewtok_kernel (tcgen05; ob_gemm_decode_kernel, the mma.sp form, for n <= 8 at 4096 x 4096)", "bound": "hbm", "peak_gbs": peaks["hbm_gbs"], "cases": out,
+    return {"kernel": "ob_gemm_fewtok_kernel (tcgen05; ob_gemm_decode_kernel, the mma.sp form, for n <= 8 at 4096 x 4096 and n = 1 at 4096 x 11008)", "bound": "hbm", "peak_gbs": peaks["hbm_gbs"], "cases": out,
             "note": "CUDA-graph replay of back-to-back calls over a weight pool > 2 x L2 (every call streams its weights "
                     "from HBM; consecutive calls overlap through programmatic dependent launch). The three 7B-class "
                     "shapes move 3-9 MB per call, less than a launch and a DRAM round trip cost at HBM speed; the "
