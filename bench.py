@@ -300,6 +300,19 @@ def decode_loop_extras(ob, dev):
         r["frac_of_measured_hbm"] = round(r["weight_gbs"] / peaks["hbm_gbs"], 4)
         out["cases"].append({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})
     del stack
+    # the same blocks with q/k/v and gate/up as one layer each (12288 x 4096, 22016 x 4096): 4 GEMMs per block
+    torch.cuda.empty_cache()
+    stack = LlamaShapedStack(blocks=4, hidden=4096, intermediate=11008, device=dev, seed=1, fused=True)
+    ob.replace_linear_layers(stack)
+    out["fused_projections_note"] = ("q/k/v as one 12288 x 4096 layer and gate/up as one 22016 x 4096 layer, 16 GEMMs instead of 28: "
+                                     "slower, not faster, with this kernel -- 172 row blocks x 32 k tiles fill 172 of the 296 CTA "
+                                     "slots and no K split fits a wave, where two 11008 x 4096 calls run 258 CTAs of 11 tiles each")
+    out["fused_projections"] = []
+    for tokens in (1, 8):
+        r = measure_decode(stack, 4096, tokens=tokens, steps=30, device=dev)
+        r["frac_of_measured_hbm"] = round(r["weight_gbs"] / peaks["hbm_gbs"], 4)
+        out["fused_projections"].append({k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})
+    del stack
     torch.cuda.empty_cache()
     return out
 

@@ -21,29 +21,47 @@ import torch.nn.functional as F
 
 
 class LlamaShapedBlock(nn.Module):
-    """The seven linear layers of a Llama-style decoder block (no biases, like the original)."""
+    """The seven linear layers of a Llama-style decoder block (no biases, like the original).
 
-    def __init__(self, hidden: int = 4096, intermediate: int = 11008, dtype=torch.float16, device=None):
+    With ``fused=True`` the three projections that read the same input are one layer (``qkv_proj``, 3 * hidden rows) and
+    so are gate and up (``gate_up_proj``, 2 * intermediate rows), as serving stacks lay them out: four GEMMs per
+    block instead of seven, each with more row blocks to spread over the SMs. The arithmetic is the same."""
+
+    def __init__(self, hidden: int = 4096, intermediate: int = 11008, dtype=torch.float16, device=None, fused: bool = False):
         super().__init__()
         kw = dict(bias=False, dtype=dtype, device=device)
-        self.q_proj, self.k_proj = nn.Linear(hidden, hidden, **kw), nn.Linear(hidden, hidden, **kw)
-        self.v_proj, self.o_proj = nn.Linear(hidden, hidden, **kw), nn.Linear(hidden, hidden, **kw)
-        self.gate_proj, self.up_proj = nn.Linear(hidden, intermediate, **kw), nn.Linear(hidden, intermediate, **kw)
+        self.fused, self.hidden, self.intermediate = fused, hidden, intermediate
+        if fused:
+            self.qkv_proj = nn.Linear(hidden, 3 * hidden, **kw)
+            self.gate_up_proj = nn.Linear(hidden, 2 * intermediate, **kw)
+        else:
+            self.q_proj, self.k_proj = nn.Linear(hidden, hidden, **kw), nn.Linear(hidden, hidden, **kw)
+            self.v_proj = nn.Linear(hidden, hidden, **kw)
+            self.gate_proj, self.up_proj = nn.Linear(hidden, intermediate, **kw), nn.Linear(hidden, intermediate, **kw)
+        self.o_proj = nn.Linear(hidden, hidden, **kw)
         self.down_proj = nn.Linear(intermediate, hidden, **kw)
 
     def forward(self, x):
         """x: (tokens, hidden). Element-wise glue stands in for attention and normalisation."""
-        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        if self.fused:
+            q, k, v = self.qkv_proj(x).split(self.hidden, dim=-1)
+        else:
+            q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         h = x + self.o_proj(torch.tanh(q) * torch.sigmoid(k) + 0.5 * v)
         h = h * torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + 1e-5).to(h.dtype)
-        return h + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
+        if self.fused:
+            gate, up = self.gate_up_proj(h).split(self.intermediate, dim=-1)
+        else:
+            gate, up = self.gate_proj(h), self.up_proj(h)
+        return h + self.down_proj(F.silu(gate) * up)
 
 
 class LlamaShapedStack(nn.Module):
-    def __init__(self, blocks: int = 4, hidden: int = 4096, intermediate: int = 11008, dtype=torch.float16, device=None, seed: int = 0):
+    def __init__(self, blocks: int = 4, hidden: int = 4096, intermediate: int = 11008, dtype=torch.float16, device=None, seed: int = 0,
+                 fused: bool = False):
         super().__init__()
         self.hidden, self.intermediate = hidden, intermediate
-        self.blocks = nn.ModuleList([LlamaShapedBlock(hidden, intermediate, dtype, device) for _ in range(blocks)])
+        self.blocks = nn.ModuleList([LlamaShapedBlock(hidden, intermediate, dtype, device, fused) for _ in range(blocks)])
         g = torch.Generator(device="cpu")
         g.manual_seed(seed)
         with torch.no_grad():

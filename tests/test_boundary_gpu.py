@@ -193,6 +193,21 @@ def test_llama_shaped_stack_replace_and_graph_decode_loop():
         _lib.check(_lib.load().onebit_check_device_status())
     m = measure_decode(stack, hidden, tokens=1, steps=5)
     assert m["linear_layers"] == 14 and m["us_per_step"] > 0
+    # q/k/v and gate/up as one layer each: the same weights stacked give the same activations (every output row is
+    # its own dot product, whatever matrix it sits in; the K split and with it the fp32 summation order may differ)
+    fused = LlamaShapedStack(blocks=2, hidden=hidden, intermediate=inter, device="cuda", seed=5, fused=True)
+    plain = LlamaShapedStack(blocks=2, hidden=hidden, intermediate=inter, device="cuda", seed=5)
+    with torch.no_grad():
+        for fb, pb in zip(fused.blocks, plain.blocks):
+            fb.qkv_proj.weight.copy_(torch.cat([pb.q_proj.weight, pb.k_proj.weight, pb.v_proj.weight]))
+            fb.gate_up_proj.weight.copy_(torch.cat([pb.gate_proj.weight, pb.up_proj.weight]))
+            fb.o_proj.weight.copy_(pb.o_proj.weight)
+            fb.down_proj.weight.copy_(pb.down_proj.weight)
+    assert ob.replace_linear_layers(fused) == 8 and ob.replace_linear_layers(plain) == 14
+    x = torch.randn((4, hidden), device="cuda").to(torch.float16)
+    with torch.no_grad():
+        yf, yp = fused(x).float(), plain(x).float()
+    assert (yf - yp).abs().max().item() <= 1e-2 * yp.abs().max().item() + 1e-3
 
 
 def test_pitched_copy_helper_moves_a_column_panel_both_ways():
