@@ -318,10 +318,16 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     const int row = q * 32 + lane;
     const uint32_t a_col = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kTmemA + 64 * grp);
     // one word of 32 sign bits -> 16 registers of two fp16 +-1 each: bit p to bit 15, bit p + 16 to bit 31
-    auto expand_word = [&](uint32_t w, uint32_t* v) {
+    // one tile row = two words of 32 sign bits -> 32 registers of two fp16 +-1 each: bit p of a word to bit 15, bit
+    // p + 16 to bit 31 of its register p. All multiplies first, then all logic operations: left to itself the compiler
+    // paired each multiply with its dependent logic operation and the chain ran at the instructions' latency.
+    auto expand_tile = [&](uint2 w, uint32_t (&v)[32]) {
 #pragma unroll
-      for (int p = 0; p < 15; ++p) v[p] = ((w * a.pow2[p]) & 0x80008000u) ^ 0xBC00BC00u;
-      v[15] = (w & 0x80008000u) ^ 0xBC00BC00u;
+      for (int p = 0; p < 15; ++p) { v[p] = w.x * a.pow2[p]; v[16 + p] = w.y * a.pow2[p]; }
+      v[15] = w.x;
+      v[31] = w.y;
+#pragma unroll
+      for (int p = 0; p < 32; ++p) asm volatile("lop3.b32 %0, %0, 0x80008000, 0xBC00BC00, 0x6A;" : "+r"(v[p]));   // (v & mask) ^ (-1.0h, -1.0h)
     };
     int s = 0;
 #pragma unroll 1
@@ -352,15 +358,13 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
         if (two) w1 = *reinterpret_cast<const uint2*>(sw + OB_TILE_BITS_BYTES);
         OB_TRACE_TILE(2, r * KL + 2 * grp);
         uint32_t v[32];
-        expand_word(w0.x, v);                                 // before the wait: only the store needs the slot
-        expand_word(w0.y, v + 16);
+        expand_tile(w0, v);                                   // before the wait: only the store needs the slot
         WORKER_WAIT(bar_aempty(grp), (r & 1) ^ 1, 203);       // the MMAs that read this pair of slots a round ago are done
         __syncwarp();        // the tcgen05 instructions below are .sync.aligned: no lane may still be in the wait loop
         tcgen05_fence_after();
         tcgen05_st_32x32b_x32_nowait(a_col, v);
         if (two) {
-          expand_word(w1.x, v);
-          expand_word(w1.y, v + 16);
+          expand_tile(w1, v);
           tcgen05_st_32x32b_x32_nowait(a_col + 32, v);
         }
         tcgen05_wait_st();
