@@ -386,21 +386,19 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     }
   } else {
     // ---------------- MMA issuer ----------------
-    // The whole warp walks the loop and one elected lane does the work of an iteration inside a single
-    // elect.sync block: wait for the tile's operand, copy its metadata, issue its four MMAs, commit. Under the
-    // elect predicate the operands of the tcgen05 instructions (descriptors, tensor-memory addresses) are
-    // warp-uniform values; issued from a branch on the lane number every instruction cost 60-75 cycles, and with
-    // all 32 lanes polling the barrier and a warp barrier per tile an iteration took 650 cycles.
     // M = 128, N = 16, sparse, fp32 accumulate; B is K-major (bit 16 clear) or N-major (bit 16 set)
     const uint32_t idesc = (1u << 2) | (1u << 4) | (kmajor ? 0u : (1u << 16)) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     // no-swizzle core matrices: 128 bytes between 8-k groups (leading offset), 2048 between the two token groups
     // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
     const uint64_t tok_desc = make_desc(0, 128, (NG == 2) ? 2048u : 0u, kLayoutNone);
     const uint64_t meta_desc = make_desc(0, 128, 128, kLayoutNone);
-    // One elect.sync for the whole loop: the elected lane runs it alone (a reconvergence of the warp after every
-    // pair of tiles cost ~400 cycles), and under the elect predicate the operands of the tcgen05 instructions stay
-    // warp-uniform values.
-    if (elect_one()) {
+    // The whole warp walks the loop, converged: all lanes wait on the barriers and work out the same descriptors and
+    // tensor-memory addresses, which the compiler can therefore keep as warp-uniform values; only the tcgen05
+    // instructions themselves are predicated on one elected lane. With the elected lane running the loop alone every
+    // operand had to be moved to the uniform datapath per instruction (30-45 cycles per tcgen05 instruction;
+    // 25600^2, n = 1: 50.9 us against 47.6 us this way); issued from a branch on the lane number it was 60-75.
+    const bool leader = elect_one();
+    {
       int s = 0, rph = 0;                                     // ring slot and phase of the round
 #pragma unroll 1
       for (int r = 0; r < nrounds; ++r) {
@@ -421,24 +419,24 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
             if (j < nt) {
               const int t = r * KL + j, x = t & (kASlots - 1);
               const uint32_t e_col = tmem_base + kTmemE + 4 * x;
-              tcgen05_cp_128x128b(e_col, meta_desc | desc_addr(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES));
+              if (leader) tcgen05_cp_128x128b(e_col, meta_desc | desc_addr(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES));
               OB_TRACE_TILE(6, t);
               const uint64_t tok = tok_desc | desc_addr(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens);
 #pragma unroll
               for (int kb = 0; kb < 4; ++kb) {
-                tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * x + 8 * kb, tok + (uint64_t)(32 * kb),
-                                      e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
+                if (leader) tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * x + 8 * kb, tok + (uint64_t)(32 * kb),
+                                                  e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
                 OB_TRACE_TILE(7 + kb, t);
               }
             }
           }
-          tcgen05_commit(bar_aempty(y));
+          if (leader) tcgen05_commit(bar_aempty(y));
           OB_TRACE_TILE(5, 2 * P);
         }
-        tcgen05_commit(bar_wempty(s));                         // the round's weights and tokens are free again
+        if (leader) tcgen05_commit(bar_wempty(s));             // the round's weights and tokens are free again
         if (++s == kRing) { s = 0; rph ^= 1; }
       }
-      tcgen05_commit(bar_acc);
+      if (leader) tcgen05_commit(bar_acc);
     }
   }
   __syncwarp();
