@@ -124,11 +124,21 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
-__device__ __forceinline__ void tcgen05_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+// Four 32-lane x 8-column loads from tensor memory in flight together, one wait for all of them. One asm block: the
+// results may not be touched before the wait, and only a data dependency on the block tells the compiler so.
+__device__ __forceinline__ void tcgen05_ld_32x32b_x8_four(uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3, uint32_t (&r)[4][8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%32];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8, %9, %10, %11, %12, %13, %14, %15}, [%33];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%16, %17, %18, %19, %20, %21, %22, %23}, [%34];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%24, %25, %26, %27, %28, %29, %30, %31}, [%35];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=&r"(r[0][0]), "=&r"(r[0][1]), "=&r"(r[0][2]), "=&r"(r[0][3]), "=&r"(r[0][4]), "=&r"(r[0][5]), "=&r"(r[0][6]), "=&r"(r[0][7]),
+        "=&r"(r[1][0]), "=&r"(r[1][1]), "=&r"(r[1][2]), "=&r"(r[1][3]), "=&r"(r[1][4]), "=&r"(r[1][5]), "=&r"(r[1][6]), "=&r"(r[1][7]),
+        "=&r"(r[2][0]), "=&r"(r[2][1]), "=&r"(r[2][2]), "=&r"(r[2][3]), "=&r"(r[2][4]), "=&r"(r[2][5]), "=&r"(r[2][6]), "=&r"(r[2][7]),
+        "=&r"(r[3][0]), "=&r"(r[3][1]), "=&r"(r[3][2]), "=&r"(r[3][3]), "=&r"(r[3][4]), "=&r"(r[3][5]), "=&r"(r[3][6]), "=&r"(r[3][7])
+      : "r"(t0), "r"(t1), "r"(t2), "r"(t3)
+      : "memory");
 }
 
 // 16 bytes into the shared memory of a CTA of the cluster; the store completes on that CTA's mbarrier (16 bytes of
@@ -455,15 +465,23 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     const int q = warp & 3, grp = warp >> 2;
     if (grp < NG) {
       const int row = q * 32 + lane;
+      // the per-row constants of an unsplit block: on their way while the last MMAs complete
+      const int64_t grow = mb * 128 + row;
+      float scale = 1.f, bias = 0.f;
+      if (S == 1) {
+        if (a.scale) scale = __half2float(a.scale[grow]);
+        if (a.bias) bias = __half2float(a.bias[grow]);
+      }
       mbar_wait(bar_acc, 0, budget, &g_fewtok_status, 208);
       __syncwarp();          // .sync.aligned loads follow
       tcgen05_fence_after();
       // the four accumulators, added in a fixed order
       float v[8];
       {
+        static_assert(kAccs == 4, "the epilogue reads four accumulators");
         uint32_t u[kAccs][8];
-#pragma unroll
-        for (int c = 0; c < kAccs; ++c) tcgen05_ld_32x32b_x8(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(16 * c + 8 * grp), u[c]);
+        const uint32_t acc0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(8 * grp);
+        tcgen05_ld_32x32b_x8_four(acc0, acc0 + 16, acc0 + 32, acc0 + 48, u);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           v[j] = (__uint_as_float(u[0][j]) + __uint_as_float(u[1][j])) + (__uint_as_float(u[2][j]) + __uint_as_float(u[3][j]));
@@ -471,8 +489,6 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       tcgen05_fence_before();
       OB_TRACE_EV(5);
       if (S == 1) {
-        const int64_t grow = mb * 128 + row;
-        const float scale = a.scale ? __half2float(a.scale[grow]) : 1.f, bias = a.bias ? __half2float(a.bias[grow]) : 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) finish(grow, 8 * grp + j, v[j], scale, bias);
       } else {
