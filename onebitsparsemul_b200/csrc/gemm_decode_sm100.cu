@@ -16,8 +16,10 @@
 //     sums of a CTA ever meet in shared memory, no warp reads token fragments, and the legacy mma.sp issue
 //     cost (one instruction per 16 x 32 weights and 8 tokens) is gone;
 //   * tokens are staged by the worker warps (through registers, or with up to 8 tokens as asynchronous 16-byte
-//     copies that nobody but the MMA thread waits for) as the B operand in the canonical no-swizzle layout: core
-//     matrices of 8 x 16 bytes. Token rows that are contiguous in k (x (n, k), or a single token) become a
+//     copies), each group of 4 warps the tokens of its own pair of tiles, so that the group's one arrival per pair
+//     hands over operand slots and tokens together and the MMA warp waits on one barrier per pair and on nothing
+//     else (every barrier wait of that warp costs ~100 cycles of its serial instruction stream, which set the
+//     CTA's pace). They form the B operand in the canonical no-swizzle layout: core matrices of 8 x 16 bytes. Token rows that are contiguous in k (x (n, k), or a single token) become a
 //     K-major operand; B (k, n) rows become an N-major operand, 16 bytes = 8 tokens of one k row per piece,
 //     so nothing is ever transposed element by element. Token columns beyond n are never written: what
 //     the tensor core reads there only reaches accumulator columns that are never stored;
@@ -91,7 +93,7 @@ template <int NG> struct FewTokCfg {
   static constexpr int kWeights = kRing * kRoundWeights;
   static constexpr int kTokens = kRing * kRoundTokens;
   static constexpr int kRecv = 136 * NP * 4;                                  // [source rank][row of this CTA's share][token]; S x ceil(128 / S) <= 133 rows
-  static constexpr int kBars = 8 * (3 * kRing + 2 * kPairs + 2) + 8;          // barriers + the tensor-memory address
+  static constexpr int kBars = 8 * (2 * kRing + 2 * kPairs + 2) + 8;          // barriers + the tensor-memory address
   static constexpr int kNeeded = kWeights + kTokens + kRecv + kBars + 1024;   // + alignment slack
   static constexpr int kTotal = kNeeded < kMinSmem ? kMinSmem : kNeeded;
   static constexpr int kPieces = KL * 128 * NP / 8 / kWorkers;                // 16-byte token pieces per worker and round
@@ -171,10 +173,9 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   const uint32_t bar0 = smem_base + L::kWeights + L::kTokens + L::kRecv;
   auto bar_wfull = [&](int s) { return bar0 + 8 * s; };                        // a round of weights has landed
   auto bar_wempty = [&](int s) { return bar0 + 8 * (kRing + s); };             // its MMAs are done: weights and tokens free
-  auto bar_tfull = [&](int s) { return bar0 + 8 * (2 * kRing + s); };          // its tokens are staged (8 warps)
-  auto bar_afull = [&](int y) { return bar0 + 8 * (3 * kRing + y); };          // both operand slots of pair y written (the 4 warps of group y)
-  auto bar_aempty = [&](int y) { return bar0 + 8 * (3 * kRing + kPairs + y); };    // the MMAs reading pair y are done
-  const uint32_t bar_acc = bar0 + 8 * (3 * kRing + 2 * kPairs);
+  auto bar_afull = [&](int y) { return bar0 + 8 * (2 * kRing + y); };          // pair y of a round is ready: both operand slots written and the pair's tokens staged (the 4 warps of group y)
+  auto bar_aempty = [&](int y) { return bar0 + 8 * (2 * kRing + kPairs + y); };    // the MMAs reading pair y are done
+  const uint32_t bar_acc = bar0 + 8 * (2 * kRing + 2 * kPairs);
   const uint32_t bar_recv = bar_acc + 8;                                       // every slice's sums for this CTA's rows have landed
   const uint32_t tmem_slot = bar_recv + 8;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem + (tmem_slot - smem_base));
@@ -217,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
       const int npre = min(nrounds, kRing);
       for (int r = 0; r < npre; ++r) issue(r);
-      for (int s = 0; s < kRing; ++s) { mbar_init(bar_wempty(s), 1); mbar_init(bar_tfull(s), tok_async ? kWorkers : kWorkers / 32); }
+      for (int s = 0; s < kRing; ++s) mbar_init(bar_wempty(s), 1);
       for (int y = 0; y < kPairs; ++y) { mbar_init(bar_afull(y), kWorkers / 64); mbar_init(bar_aempty(y), 1); }
       mbar_init(bar_acc, 1);
       mbar_init(bar_recv, 1);
@@ -237,18 +238,24 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   // Everything that does not depend on the round is worked out once: the source of the piece in the slice's first
   // round (it then moves on by a fixed stride per round), its place inside a round's staging area, the tile of the
   // round it belongs to (a slice's last round may be short) and whether its tokens exist at all.
+  // The tokens of a pair of tiles are staged by the worker group that expands that pair (threads 128 g .. 128 g + 127
+  // take tiles 2 g and 2 g + 1 of every round), so that the group's arrival on the pair's "ready" barrier covers them
+  // and the MMA warp waits for one barrier per pair and nothing else.
+  static_assert(KL == 2 * kPairs && kWorkers == 128 * kPairs, "a group of 128 workers stages the tokens of its two tiles");
+  auto piece_index = [&](int i) { return (tid & 127) + 128 * i; };   // among the pieces of this thread's group
+  const int tgrp = (tid >> 7) & 1;
   uint32_t tsrc[kPieces];                                     // element offset from a.b (the launcher checks n * k < 2^31)
   uint32_t tplace[kPieces];                                   // bits 0-23: byte offset in the staging area, 24-31: tile
 #pragma unroll
   for (int i = 0; i < kPieces; ++i) {
-    const int idx = tid + kWorkers * i;
+    const int idx = piece_index(i);
     if (kmajor) {
-      const int j = idx % NP, c = idx / NP;                   // token, 8-k chunk of the round (16 chunks per tile)
+      const int j = idx % NP, c = 32 * tgrp + idx / NP;       // token, 8-k chunk of the round (16 chunks per tile)
       const int tile = (j < nvalid) ? (c >> 4) : KL;          // KL = never
       tsrc[i] = (uint32_t)((n0 + j) * a.k + (int64_t)tile_begin * OB_TILE_K + c * 8);
       tplace[i] = (uint32_t)((c >> 4) * L::kTileTokens + (j >> 3) * 2048 + (c & 15) * 128 + (j & 7) * 16) | ((uint32_t)tile << 24);
     } else {
-      const int kk = idx / NG, ng = idx % NG;                 // k row of the round, token group
+      const int kk = 256 * tgrp + idx / NG, ng = idx % NG;    // k row of the round, token group
       const int tile = (8 * ng < nvalid) ? (kk >> 7) : KL;
       tsrc[i] = (uint32_t)(((int64_t)tile_begin * OB_TILE_K + kk) * a.n + n0 + 8 * ng);
       tplace[i] = (uint32_t)((kk >> 7) * L::kTileTokens + ng * 2048 + (kk & 127) * 16) | ((uint32_t)tile << 24);
@@ -265,12 +272,12 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
         if (kmajor || vec_rows) {
           tv[i] = __ldg(reinterpret_cast<const uint4*>(src));
         } else if (quad_rows) {
-          const int ng = (tid + kWorkers * i) % NG;
+          const int ng = piece_index(i) % NG;
           uint2* h4 = reinterpret_cast<uint2*>(&tv[i]);       // n % 4 == 0: whole groups of four tokens
           h4[0] = __ldg(reinterpret_cast<const uint2*>(src));
           if (8 * ng + 4 < nvalid) h4[1] = __ldg(reinterpret_cast<const uint2*>(src + 4));
         } else {
-          const int ng = (tid + kWorkers * i) % NG;
+          const int ng = piece_index(i) % NG;
           __half* h = reinterpret_cast<__half*>(&tv[i]);
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj)
@@ -290,9 +297,8 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
 
   // Whole 16-byte pieces (token rows contiguous in k, or B (k, n) with n % 8 == 0) do not pass through registers at
   // all: every worker issues its pieces of a round as asynchronous 16-byte copies (cp.async) at the top of the round and
-  // lets them arrive on the round's token barrier (cp.async.mbarrier.arrive.noinc, one arrival per worker thread); nobody
-  // waits for a token except the MMA thread, which orders the copies' generic-proxy writes before the tensor core's
-  // reads with a proxy fence after its wait. Other alignments and token counts keep the register route.
+  // waits for them only after it has expanded its pair of tiles, right before it arrives on the pair's barrier (by then
+  // they have long landed). Other alignments and token counts keep the register route.
   auto issue_tokens_async = [&](int r) {
     const int ntile = min(KL, T - r * KL);
     const uint32_t sb = smem_base + L::kWeights + (r % kRing) * L::kRoundTokens;
@@ -302,7 +308,6 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sb + (tplace[i] & 0xFFFFFFu)), "l"(a.b + tsrc[i]) : "memory");
       tsrc[i] += tstride;
     }
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_tfull(r % kRing)) : "memory");
   };
   uint4 tv[kPieces];
   if (warp < 8) {
@@ -345,14 +350,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       OB_TRACE_ROUND(12, r);
       if (r >= kRing) WORKER_WAIT(bar_wempty(s), ((r / kRing) - 1) & 1, 201);   // the round that used this slot is multiplied
       if (tok_async) {
-        // this round's tokens set off now; the MMA thread needs them only after the round's first pair is expanded
+        // the tokens of this group's pair set off now; they are needed only when the pair is handed to the MMA warp
         issue_tokens_async(r);
       } else {
         OB_TRACE_ROUND(13, r);
-        store_tokens(r, tv);
-        fence_proxy_async();                                  // the tensor core reads them through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tfull(s));
+        store_tokens(r, tv);                                  // handed over with the pair (proxy fence and arrival below)
         OB_TRACE_ROUND(14, r);
         if (r + 1 < nrounds) fetch_tokens(r + 1, tv);         // in flight while this round is expanded
       }
@@ -379,6 +381,10 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
         }
         tcgen05_wait_st();
         tcgen05_fence_before();
+        // the pair's tokens: this thread's copies have landed (or were stored at the top of the round); the tensor
+        // core reads them through the async proxy
+        if (tok_async) asm volatile("cp.async.wait_all;" ::: "memory");
+        fence_proxy_async();
         OB_TRACE_TILE(3, r * KL + 2 * grp);
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_afull(grp));
@@ -409,13 +415,12 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     // 25600^2, n = 1: 50.9 us against 47.6 us this way); issued from a branch on the lane number it was 60-75.
     const bool leader = elect_one();
     {
-      int s = 0, rph = 0;                                     // ring slot and phase of the round
+      int s = 0;                                              // ring slot of the round
 #pragma unroll 1
       for (int r = 0; r < nrounds; ++r) {
         const int nt = min(KL, T - r * KL);
-        mbar_wait_sleepy(bar_tfull(s), rph, kPollNs, budget, &g_fewtok_status, 205);
-        fence_proxy_async();                                  // tokens written by cp.async (generic proxy) -> the tensor core's reads
-        mbar_wait_sleepy(bar_wfull(s), rph, kPollNs, budget, &g_fewtok_status, 206);
+        // No wait for the round's weights or tokens here: a pair's barrier completes only after its four worker warps
+        // have seen the weights land (they read the sign bits) and have staged and fenced the pair's tokens.
 #pragma unroll 1
         for (int pp = 0; 2 * pp < nt; ++pp) {
           const int P = r * (KL / 2) + pp, y = P & 1;
@@ -444,7 +449,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
           OB_TRACE_TILE(5, 2 * P);
         }
         if (leader) tcgen05_commit(bar_wempty(s));             // the round's weights and tokens are free again
-        if (++s == kRing) { s = 0; rph ^= 1; }
+        if (++s == kRing) s = 0;
       }
       if (leader) tcgen05_commit(bar_acc);
     }
