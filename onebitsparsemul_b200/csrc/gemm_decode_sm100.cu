@@ -415,38 +415,47 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     // 25600^2, n = 1: 50.9 us against 47.6 us this way); issued from a branch on the lane number it was 60-75.
     const bool leader = elect_one();
     {
+      static_assert(KL == 4 && kPairs == 2 && kASlots == 4, "pair pp of a round is barrier pair pp and operand slots 2 pp, 2 pp + 1");
       int s = 0;                                              // ring slot of the round
+      // Whether the next pair is ready is asked BEFORE the commit of the pair in hand: the answer travels while the
+      // commit is issued, and the workers are normally ahead, so that the warp rarely stands at a barrier at all.
+      bool ready = false;
 #pragma unroll 1
       for (int r = 0; r < nrounds; ++r) {
         const int nt = min(KL, T - r * KL);
         // No wait for the round's weights or tokens here: a pair's barrier completes only after its four worker warps
         // have seen the weights land (they read the sign bits) and have staged and fenced the pair's tokens.
-#pragma unroll 1
-        for (int pp = 0; 2 * pp < nt; ++pp) {
-          const int P = r * (KL / 2) + pp, y = P & 1;
-          OB_TRACE_TILE(11, 2 * P);
-          mbar_wait_sleepy(bar_afull(y), (P >> 1) & 1, kPollNs, budget, &g_fewtok_status, 207);
-          OB_TRACE_TILE(4, 2 * P);
-          tcgen05_fence_after();
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int j = 2 * pp + h;
-            if (j < nt) {
-              const int t = r * KL + j, x = t & (kASlots - 1);
-              const uint32_t e_col = tmem_base + kTmemE + 4 * x;
-              if (leader) tcgen05_cp_128x128b(e_col, meta_desc | desc_addr(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES));
-              OB_TRACE_TILE(6, t);
-              const uint64_t tok = tok_desc | desc_addr(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens);
+        for (int pp = 0; pp < KL / 2; ++pp) {
+          if (2 * pp < nt) {
+            OB_TRACE_TILE(11, r * KL + 2 * pp);
+            if (!ready) mbar_wait_sleepy(bar_afull(pp), r & 1, kPollNs, budget, &g_fewtok_status, 207);
+            OB_TRACE_TILE(4, r * KL + 2 * pp);
+            tcgen05_fence_after();
 #pragma unroll
-              for (int kb = 0; kb < 4; ++kb) {
-                if (leader) tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * x + 8 * kb, tok + (uint64_t)(32 * kb),
-                                                  e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
-                OB_TRACE_TILE(7 + kb, t);
+            for (int h = 0; h < 2; ++h) {
+              const int j = 2 * pp + h;
+              if (j < nt) {
+                const int t = r * KL + j;
+                const uint32_t e_col = tmem_base + kTmemE + 4 * j;
+                if (leader) tcgen05_cp_128x128b(e_col, meta_desc | desc_addr(smem_base + s * L::kRoundWeights + j * OB_TILE_META_BYTES));
+                OB_TRACE_TILE(6, t);
+                const uint64_t tok = tok_desc | desc_addr(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens);
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+                  if (leader) tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * j + 8 * kb, tok + (uint64_t)(32 * kb),
+                                                    e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
+                  OB_TRACE_TILE(7 + kb, t);
+                }
               }
             }
+            // the pair that follows: pair 1 of this round, or pair 0 of the next one
+            ready = false;
+            if (pp == 0) { if (2 < nt) ready = mbar_try_wait(bar_afull(1), r & 1); }
+            else if (r + 1 < nrounds) ready = mbar_try_wait(bar_afull(0), (r + 1) & 1);
+            if (leader) tcgen05_commit(bar_aempty(pp));
+            OB_TRACE_TILE(5, r * KL + 2 * pp);
           }
-          if (leader) tcgen05_commit(bar_aempty(y));
-          OB_TRACE_TILE(5, 2 * P);
         }
         if (leader) tcgen05_commit(bar_wempty(s));             // the round's weights and tokens are free again
         if (++s == kRing) s = 0;
