@@ -348,7 +348,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
 #pragma unroll 1
     for (int r = 0; r < nrounds; ++r) {
       OB_TRACE_ROUND(12, r);
-      if (r >= kRing) WORKER_WAIT(bar_wempty(s), ((r / kRing) - 1) & 1, 201);   // the round that used this slot is multiplied
+      // The token slot of this round was last read by this group's pair of round r - kRing. No wait for it: in round
+      // r - 1 this warp has seen the commit that followed its pair of round r - 2 (the wait before the tensor-memory
+      // stores below), and a commit completes only after every MMA issued before it, those of round r - kRing
+      // (kRing >= 3) among them.
+      static_assert(kRing >= 3, "the pair barrier seen a round ago must cover the round that used the token slot");
       if (tok_async) {
         // the tokens of this group's pair set off now; they are needed only when the pair is handed to the MMA warp
         issue_tokens_async(r);
