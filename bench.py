@@ -203,7 +203,7 @@ def run_reference(args):
             "config": {"workload": workload_name(args.size, args.gpus), "sample": sample},
             "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cpu.cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit_line(line)
 
 
 # ---- our arm ---------------------------------------------------------------------------------------------------
@@ -619,9 +619,27 @@ def run_ours(args):
             line["decode_loop"] = decode_loop
         if context is not None:
             line["context"] = context
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+_LINE_OUT = None
+
+
+def claim_stdout():
+    """Keeps the process's standard output for the one JSON line: whatever else writes to file descriptor 1 from here
+    on (a library's banner, e.g. NCCL's version line when NCCL_DEBUG is set; a stray print) goes to standard error."""
+    global _LINE_OUT
+    sys.stdout.flush()
+    _LINE_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit_line(line):
+    out = _LINE_OUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
@@ -634,6 +652,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the supplementary decode-regime numbers")
     ap.add_argument("--no-square8192", action="store_true", help="skip the supplementary 8192^3 figure")
     args = ap.parse_args()
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -164,3 +164,23 @@ def test_gemm_against_the_references_own_host_gemm():
     weights = (np.arange(m * n) % 7 + 1).astype(np.float64)
     assert float((c32.reshape(-1).astype(np.float64) * weights).sum()) == checksum
     assert (c32 == A.astype(np.float32) @ B.astype(np.float32)).all()
+
+
+def test_bench_reference_arm_prints_one_json_line():
+    # the reference arm of bench.py (the oracle port on the host cores): exactly one line on standard output, a JSON
+    # object with the contract's keys, even when something else writes to file descriptor 1 while it runs
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--size", "512", "--steps", "1", "--warmup", "0"],
+                       capture_output=True, text=True, timeout=600, cwd=root, env=dict(os.environ, NCCL_DEBUG="VERSION"))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.splitlines()
+    assert len(lines) == 1, r.stdout[:2000]
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["unit"] == "TFLOP/s" and line["value"] > 0
+    for key in ("metric", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["cpu_baseline"]["kind"] == "port"
