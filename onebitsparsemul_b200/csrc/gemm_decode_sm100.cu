@@ -35,6 +35,7 @@
 //     resident CTA of the next grid can then never hold tensor memory that a CTA of this grid still needs.
 // Every mbarrier wait is bounded; a wait that gives up records a code in g_fewtok_status, and the kernel still
 // runs to its end and frees its tensor memory.
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -110,6 +111,7 @@ struct FewTokArgs {
   void* d;
   int64_t m, n, k;
   int fresh_weights;    // 1: request no weights before the previous kernel of the stream has completed
+  int tok_tma;          // 1: B (k, n) with 16 tokens per pass is fetched by TMA (the kernel's tensor-map argument is valid)
   uint32_t pow2[16];    // pow2[p] = 1 << (15 - p): a multiplication by a value the compiler does not know is an integer
                         // multiply-add (FMA pipe), a shift by a constant is an ALU-pipe instruction like the logic
                         // operation that follows it; the expansion is bound by the ALU pipe
@@ -152,7 +154,7 @@ __device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, float x, floa
 
 // TM = token-major operands (the nn.Linear convention): b is x (n, k) row-major, d is y (n, m) row-major
 template <int NG, typename OutT, bool TM>
-__global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(const __grid_constant__ CUtensorMap tok_map, FewTokArgs a) {
   using L = FewTokCfg<NG>;
   constexpr int NP = L::NP, kRing = L::kRing, kPieces = L::kPieces;
   extern __shared__ uint8_t smem_raw[];
@@ -194,6 +196,10 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   // whole 16-byte pieces of up to 8 tokens: staged by asynchronous copies (see below). With 16 tokens per pass the
   // register route is faster (measured: 28672 x 8192, 16 tokens: 31 us against 42 us)
   const bool tok_async = NG == 1 && (kmajor || vec_rows);
+  // B (k, n) with 16 tokens per pass: a row of the block is 32 bytes, and a TMA box of 16 tokens x 128 k rows with the
+  // 32-byte swizzle lands exactly as the tensor core's N-major 32-byte-swizzled operand -- one box per tile on the
+  // weight barrier, requested by the weight-stream thread; no worker touches a token
+  const bool tok_tma = NG == 2 && !TM && a.tok_tma != 0;
 
   // split-K hand-off: CTA o of the cluster owns rows [o * rows_per, (o+1) * rows_per) of the block and receives,
   // from every CTA of the cluster (itself included), 16-byte pieces of those rows' sums
@@ -205,9 +211,18 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     const int nt = min(KL, T - r * KL);
     const int64_t tile = mb * tiles_k + tile_begin + r * KL;
     const uint32_t dst = smem_base + s * L::kRoundWeights;
-    mbar_expect_tx(bar_wfull(s), nt * kTileBytes);
+    mbar_expect_tx(bar_wfull(s), nt * (kTileBytes + (tok_tma ? L::kTileTokens : 0)));
     bulk_load(dst, a.meta_tile + tile * OB_TILE_META_BYTES, nt * OB_TILE_META_BYTES, bar_wfull(s));
     bulk_load(dst + KL * OB_TILE_META_BYTES, a.bits_tile + tile * OB_TILE_BITS_BYTES, nt * OB_TILE_BITS_BYTES, bar_wfull(s));
+  };
+  // the round's tokens by TMA (the barrier already expects their bytes): x = first token of the block (a multiple of
+  // 16 tokens = 32 bytes), y = first k row of the tile
+  auto issue_tokens_tma = [&](int r) {
+    const int s = r % kRing;
+    const int nt = min(KL, T - r * KL);
+    for (int j = 0; j < nt; ++j)
+      tma_load_2d(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens, &tok_map, (int)n0,
+                  (tile_begin + r * KL + j) * OB_TILE_K, bar_wfull(s));
   };
   if (warp == kProdWarp) {
     // ---------------- weight stream: round r of the slice -> ring slot r % kRing ----------------
@@ -218,6 +233,11 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       if (a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
       const int npre = min(nrounds, kRing);
       for (int r = 0; r < npre; ++r) issue(r);
+      if (tok_tma) {
+        // tokens are the previous kernel's results: only after the dependency wait
+        if (!a.fresh_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
+        for (int r = 0; r < npre; ++r) issue_tokens_tma(r);
+      }
       for (int s = 0; s < kRing; ++s) mbar_init(bar_wempty(s), 1);
       for (int y = 0; y < kPairs; ++y) { mbar_init(bar_afull(y), kWorkers / 64); mbar_init(bar_aempty(y), 1); }
       mbar_init(bar_acc, 1);
@@ -312,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   uint4 tv[kPieces];
   if (warp < 8) {
     asm volatile("griddepcontrol.wait;" ::: "memory");        // the previous kernel's results (the tokens) are complete
-    if (!tok_async) fetch_tokens(0, tv);
+    if (!tok_async && !tok_tma) fetch_tokens(0, tv);
   }
   tcgen05_fence_before();
   __syncthreads();                                            // the barriers exist, the tensor-memory address is written
@@ -356,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       if (tok_async) {
         // the tokens of this group's pair set off now; they are needed only when the pair is handed to the MMA warp
         issue_tokens_async(r);
-      } else {
+      } else if (!tok_tma) {
         OB_TRACE_ROUND(13, r);
         store_tokens(r, tv);                                  // handed over with the pair (proxy fence and arrival below)
         OB_TRACE_ROUND(14, r);
@@ -402,6 +422,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
       for (int r = kRing; r < nrounds; ++r) {
         mbar_wait_sleepy(bar_wempty(r % kRing), ((r / kRing) - 1) & 1, kPollNs, budget, &g_fewtok_status, 204);
         issue(r);
+        if (tok_tma) issue_tokens_tma(r);
       }
     }
   } else {
@@ -410,7 +431,10 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
     const uint32_t idesc = (1u << 2) | (1u << 4) | (kmajor ? 0u : (1u << 16)) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     // no-swizzle core matrices: 128 bytes between 8-k groups (leading offset), 2048 between the two token groups
     // (stride offset; 0 with one group: both halves of the 16 columns then read the same tokens)
-    const uint64_t tok_desc = make_desc(0, 128, (NG == 2) ? 2048u : 0u, kLayoutNone);
+    // TMA-staged tokens: one 32-byte-swizzled atom of 16 tokens x 8 k rows every 256 bytes (stride offset), a single
+    // atom along the tokens (leading offset unused), 1024 bytes per 32-k block
+    const uint64_t tok_desc = tok_tma ? make_desc(0, 4096, 256, kLayoutSw32) : make_desc(0, 128, (NG == 2) ? 2048u : 0u, kLayoutNone);
+    const uint32_t tok_kb = tok_tma ? 64u : 32u;             // descriptor address units (16 bytes) per 32-k block
     const uint64_t meta_desc = make_desc(0, 128, 128, kLayoutNone);
     // The whole warp walks the loop, converged: all lanes wait on the barriers and work out the same descriptors and
     // tensor-memory addresses, which the compiler can therefore keep as warp-uniform values; only the tcgen05
@@ -447,7 +471,7 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
                 const uint64_t tok = tok_desc | desc_addr(smem_base + L::kWeights + s * L::kRoundTokens + j * L::kTileTokens);
 #pragma unroll
                 for (int kb = 0; kb < 4; ++kb) {
-                  if (leader) tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * j + 8 * kb, tok + (uint64_t)(32 * kb),
+                  if (leader) tcgen05_mma_sp_f16_ts(tmem_base + 16 * kb, tmem_base + kTmemA + 32 * j + 8 * kb, tok + (uint64_t)(tok_kb * kb),
                                                     e_col + (kb & ~1), idesc | (uint32_t)(kb & 1), t != 0);
                   OB_TRACE_TILE(7 + kb, t);
                 }
@@ -565,9 +589,45 @@ __global__ void __launch_bounds__(kThreads, 2) ob_gemm_fewtok_kernel(FewTokArgs 
   }
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map of B (k, n) row-major for the 16-token passes: boxes of 16 tokens x 128 k rows, 32-byte swizzle, zero
+// fill beyond n. False if this B cannot be described or the route is not taken (then the workers stage the tokens).
+// Measured (us per call, workers / TMA): 25600^2 in 4 slices 55.0 / 47.8, 11008 x 4096 in 3 slices 7.7 / 7.5,
+// 4096 x 11008 in 8 slices 7.8 / 7.7, but 28672 x 8192 unsplit 23.2 / 26.8 (every CTA asks L2 for the same token rows
+// at the same time, 32 bytes per request, and TMA does not go through the L1 the two CTAs of an SM share) and
+// 4096^2 in 8 slices of 4 tiles 5.6 / 5.8 (a slice of one round: 256 threads fetch it faster than one box per tile).
+// Hence: only with a K split and slices of at least two rounds. ONEBIT_FEWTOK_TMA = 0 / 1 forces it off / on.
+bool make_token_map(CUtensorMap* map, const void* b, int64_t n, int64_t k, int S) {
+  static const int forced = [] { const char* v = getenv("ONEBIT_FEWTOK_TMA"); return v ? (atoi(v) != 0 ? 1 : 0) : -1; }();
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (forced == 0 || !encode || n % 8 != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0) return false;
+  if (forced != 1 && (S < 2 || k / OB_TILE_K / S < 2 * KL)) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)n, (cuuint64_t)k};
+  const cuuint64_t strides[1] = {(cuuint64_t)n * 2};
+  const cuuint32_t box[2] = {16, (cuuint32_t)OB_TILE_K};
+  const cuuint32_t estr[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(b), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int NG, typename OutT, bool TM>
-cudaError_t launch(const FewTokArgs& a, int S, cudaStream_t stream) {
+cudaError_t launch(const FewTokArgs& a_in, int S, cudaStream_t stream) {
   using L = FewTokCfg<NG>;
+  FewTokArgs a = a_in;
+  CUtensorMap tok_map = {};
+  a.tok_tma = (NG == 2 && !TM && make_token_map(&tok_map, a.b, a.n, a.k, S)) ? 1 : 0;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -593,7 +653,7 @@ cudaError_t launch(const FewTokArgs& a, int S, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 2 : 1;
-  return cudaLaunchKernelEx(&cfg, ob_gemm_fewtok_kernel<NG, OutT, TM>, a);
+  return cudaLaunchKernelEx(&cfg, ob_gemm_fewtok_kernel<NG, OutT, TM>, tok_map, a);
 }
 
 // K split over a cluster of S CTAs (1..8; the slices need not be equal). Two CTAs share an SM, so a wave holds
@@ -635,7 +695,7 @@ cudaError_t launch_gemm_fewtok(const void* bits_tile, const void* meta_tile, con
                                bool fresh_weights, cudaStream_t stream) {
   FewTokArgs a{static_cast<const uint8_t*>(bits_tile), static_cast<const uint8_t*>(meta_tile),
                static_cast<const __half*>(scale), static_cast<const __half*>(bias), static_cast<const __half*>(b), d, m, n, k,
-               fresh_weights ? 1 : 0, {}};
+               fresh_weights ? 1 : 0, 0, {}};
   for (int p = 0; p < 16; ++p) a.pow2[p] = 1u << (15 - p);
   if (k * (n > 1 ? n : 1) >= (int64_t)1 << 31) return cudaErrorInvalidValue;   // token offsets are 32-bit in the kernel
   return token_major ? dispatch<true>(a, out_type, stream) : dispatch<false>(a, out_type, stream);

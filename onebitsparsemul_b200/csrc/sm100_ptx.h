@@ -157,7 +157,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
-constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2;
+constexpr uint32_t kLayoutNone = 0, kLayoutSw128 = 2, kLayoutSw32 = 6;
 
 __device__ __forceinline__ uint32_t expand_pair(uint32_t w, int j) {
   return ((w << (15 - j)) & 0x80008000u) ^ 0xBC00BC00u;
