@@ -19,7 +19,10 @@
 //     copies), each group of 4 warps the tokens of its own pair of tiles, so that the group's one arrival per pair
 //     hands over operand slots and tokens together and the MMA warp waits on one barrier per pair and on nothing
 //     else (every barrier wait of that warp costs ~100 cycles of its serial instruction stream, which set the
-//     CTA's pace). They form the B operand in the canonical no-swizzle layout: core matrices of 8 x 16 bytes. Token rows that are contiguous in k (x (n, k), or a single token) become a
+//     CTA's pace). They form the B operand in the canonical no-swizzle layout: core matrices of 8 x 16 bytes.
+//     Exception: 16 tokens per pass of B (k, n) under a K split come by TMA, one box of 16 tokens x 128 k rows with
+//     the 32-byte swizzle per tile, requested by the weight-stream thread onto the round's weight barrier (see
+//     make_token_map for where that pays). Token rows that are contiguous in k (x (n, k), or a single token) become a
 //     K-major operand; B (k, n) rows become an N-major operand, 16 bytes = 8 tokens of one k row per piece,
 //     so nothing is ever transposed element by element. Token columns beyond n are never written: what
 //     the tensor core reads there only reaches accumulator columns that are never stored;
